@@ -1,0 +1,358 @@
+// Decode-side scans over one (batch, kv head) stream of the packed cache.
+//
+// One warp owns a tensor (K or V) of a stream; lane l owns channels 4l..4l+3, i.e. one 16-byte
+// vector of every supergroup.  The stream is brought into shared memory in tiles of 32 tokens
+// by non-multicast bulk copies (1-D TMA) that complete on mbarriers; each warp runs its own
+// ring, issued by its lane 0, so no other warp can stall it.
+//
+// K warp: replays the recurrence, forms per-lane partial dot products with the query for 8
+// tokens at a time, reduces them across lanes through a shared-memory transpose, and hands the
+// logits to a sink (shared-memory ring in the fused kernel, fp16 global in forward_qk).
+// V warp: takes softmax weights for a tile (from the ring, with online softmax, or from fp16
+// global in forward_ov), replays the recurrence and accumulates weight * value.
+// Both then quantise the new token with the state the replay left (token T-1), write it into
+// slot T and add its own contribution (src/adkv/kernel/gemv.cu:744-814, 1105-1159).
+#pragma once
+#include "adkv_device.cuh"
+
+namespace adkv {
+
+constexpr int kTileTok = 32;   // tokens per tile
+constexpr int kStages = 3;     // bulk-copy ring depth per warp
+constexpr int kLogitSlots = 4; // logits ring depth (fused kernel)
+
+template <int BITS>
+struct Tile {
+    static constexpr int WORDS = kTileTok / Codec<BITS>::TPW;   // words per channel per tile
+    static constexpr int BYTES = WORDS * kD * 4;                // 4-bit: 2048, 2-bit: 1024
+};
+
+// Per-warp bulk-copy ring over the words of one stream.
+template <int BITS>
+struct StreamRing {
+    uint8_t *buf;           // kStages * Tile::BYTES, 128-byte aligned
+    uint64_t *bar;          // kStages barriers
+    const uint8_t *src;     // start of the stream in global memory
+    int n_tiles, T;
+    int wait_code;
+
+    __device__ __forceinline__ uint32_t tile_bytes(int i) const
+    {
+        const int ntok = min(kTileTok, T - i * kTileTok);
+        const int words = (ntok + Codec<BITS>::TPW - 1) / Codec<BITS>::TPW;
+        return uint32_t(words) * kD * 4;
+    }
+    // lane 0 only
+    __device__ __forceinline__ void issue(int i) const
+    {
+        const int st = i % kStages;
+        const uint32_t bytes = tile_bytes(i);
+        mbar_expect_tx(&bar[st], bytes);
+        bulk_load(buf + st * Tile<BITS>::BYTES, src + size_t(i) * Tile<BITS>::BYTES, bytes, &bar[st]);
+    }
+    __device__ __forceinline__ void prologue(int lane) const
+    {
+        if (lane == 0)
+            for (int i = 0; i < min(kStages, n_tiles); ++i) issue(i);
+    }
+    __device__ __forceinline__ bool wait(int i) const
+    {
+        return mbar_wait_bounded(&bar[i % kStages], (i / kStages) & 1, wait_code);
+    }
+    __device__ __forceinline__ const uint4 *tile(int i, int lane) const
+    {
+        return reinterpret_cast<const uint4 *>(buf + (i % kStages) * Tile<BITS>::BYTES) + lane;
+    }
+    // all lanes, after the tile has been consumed
+    __device__ __forceinline__ void release_and_refill(int i, int lane) const
+    {
+        __syncwarp();
+        if (lane == 0 && i + kStages < n_tiles) issue(i + kStages);
+    }
+    // After a failed wait: give copies already issued a bounded chance to land before the
+    // shared memory is handed back.
+    __device__ __forceinline__ void drain(int from) const
+    {
+        const int issued = min(n_tiles, from + kStages);
+        for (int i = from; i < issued; ++i)
+            if (!mbar_wait_bounded(&bar[i % kStages], (i / kStages) & 1, kStatDrain)) break;
+    }
+};
+
+// ---------------------------------------------------------------------------------- K side
+
+// Replay 8 tokens (fields J0..J0+7 of the 4 words in `w`) and accumulate the partial dot products.
+template <int BITS, int G, bool EXACT, int J0, bool PARTIAL>
+__device__ __forceinline__ void k_chunk(const uint4 &w, Chan (&ch)[4], const float (&qv)[G][4],
+                                        float (&part)[G][8], int count, float smin, float smax)
+{
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    uint32_t hi[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) hi[c] = ww[c] >> Codec<BITS>::HI_SHIFT;
+    static_for<8>([&](auto jc) {
+        constexpr int j = decltype(jc)::value;
+#pragma unroll
+        for (int g = 0; g < G; ++g) part[g][j] = 0.f;
+        if (!PARTIAL || J0 + j < count) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float q = code_f<BITS, J0 + j>(ww[c], hi[c]);
+                const float xh = replay_step<EXACT>(q, ch[c], smin, smax);
+#pragma unroll
+                for (int g = 0; g < G; ++g) part[g][j] = fmaf(qv[g][c], xh, part[g][j]);
+            }
+        }
+    });
+}
+
+// Sum part[g][0..7] over the 32 lanes through a shared-memory transpose; afterwards lane l
+// (every lane, replicated over l>>3) holds the full sum for token (l & 7) of head g.
+// red: float [8][36] of this warp, reused head after head.
+template <int G>
+__device__ __forceinline__ void reduce8(float (&part)[G][8], float *red, int lane, float (&sum)[G])
+{
+    const int row = lane & 7, cb = (lane >> 3) * 8;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) red[j * 36 + lane] = part[g][j];
+        __syncwarp();
+        const float4 a = *reinterpret_cast<const float4 *>(&red[row * 36 + cb]);
+        const float4 b = *reinterpret_cast<const float4 *>(&red[row * 36 + cb + 4]);
+        __syncwarp();
+        float s = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+        s += __shfl_xor_sync(kFull, s, 8);
+        s += __shfl_xor_sync(kFull, s, 16);
+        sum[g] = s;
+    }
+}
+
+struct KArgs {
+    const __half *q;        // [B, Hq, D]
+    uint8_t *cache;         // [B, Hkv, n_super_cap, D] words
+    const __half *x_new;    // [B, Hkv, D]
+    ParamPtrs p;
+    int Hq, Hkv, T, n_super_cap;
+    float smin, smax;
+};
+
+// Sink interface (duck-typed):
+//   bool begin_tile(int i)            wait for room; false = bounded wait gave up
+//   void put8(int i, int g, int tok_in_tile, float v, int lane)   called by lanes 0..7 with tok = base + lane
+//   void end_tile(int i, int lane)
+//   void put_self(int g, float v)     lane 0
+//   void finish(int lane)
+template <int BITS, int G, bool EXACT, class Sink>
+__device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, uint8_t *ring_buf,
+                                       uint64_t *ring_bar, float *red, Sink &sink)
+{
+    using C = Codec<BITS>;
+    const int bh = b * a.Hkv + h;
+    Chan ch[4];
+    load_chan4<EXACT>(ch, a.p, h, 4 * lane);
+    float qv[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane);
+
+    uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
+    StreamRing<BITS> ring{ring_buf, ring_bar, stream, (a.T + kTileTok - 1) / kTileTok, a.T, kStatKWait};
+    ring.prologue(lane);
+
+    bool ok = true;
+    int i = 0;
+    for (; i < ring.n_tiles; ++i) {
+        if (!(ok = ring.wait(i))) break;
+        if (!(ok = sink.begin_tile(i))) break;
+        const uint4 *tile = ring.tile(i, lane);
+        const int ntok = min(kTileTok, a.T - i * kTileTok);
+        float part[G][8], sum[G];
+        if (ntok == kTileTok) {
+#pragma unroll
+            for (int wd = 0; wd < Tile<BITS>::WORDS; ++wd) {
+                const uint4 w = tile[wd * (kD / 4)];
+#pragma unroll
+                for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
+                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false>(w, ch, qv, part, 8, a.smin, a.smax);
+                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, false>(w, ch, qv, part, 8, a.smin, a.smax);
+                    reduce8<G>(part, red, lane, sum);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
+                }
+            }
+        } else {
+            for (int wd = 0; wd * C::TPW < ntok; ++wd) {
+                const uint4 w = tile[wd * (kD / 4)];
+                const int count = ntok - wd * C::TPW;   // valid fields in this word (may exceed TPW)
+#pragma unroll
+                for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
+                    if (c8 * 8 >= count) break;
+                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, true>(w, ch, qv, part, count, a.smin, a.smax);
+                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, true>(w, ch, qv, part, count, a.smin, a.smax);
+                    reduce8<G>(part, red, lane, sum);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
+                }
+            }
+        }
+        sink.end_tile(i, lane);
+        ring.release_and_refill(i, lane);
+    }
+    if (!ok) {
+        ring.drain(i);
+        return;
+    }
+
+    // Append k_new as token T with the state left by token T-1, then its own logit from the
+    // dequantised value.
+    float xn[4], xh[4];
+    load_half4(xn, a.x_new + size_t(bh) * kD + 4 * lane);
+    uint4 *slot = reinterpret_cast<uint4 *>(stream) + size_t(a.T / C::TPW) * (kD / 4) + lane;
+    uint4 wv = *slot;
+    uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    const int sh = BITS * (a.T % C::TPW);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        float rh;
+        const float q = quantize<BITS>(xn[c], ch[c], rh);
+        xh[c] = __fadd_rn(rh, ch[c].zp);
+        ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+    }
+    *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+    if (!sink.begin_tile(ring.n_tiles)) return;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s = fmaf(qv[g][c], xh[c], s);
+        s = warp_sum(s);
+        if (lane == 0) sink.put_self(g, s);
+    }
+    sink.finish(lane);
+}
+
+// ---------------------------------------------------------------------------------- V side
+
+template <int BITS, int G, bool EXACT, int J0, bool PARTIAL>
+__device__ __forceinline__ void v_chunk(const uint4 &w, Chan (&ch)[4], const float *wts /* [G][32] smem */,
+                                        int tok0, float (&acc)[G][4], int count, float smin, float smax)
+{
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    uint32_t hi[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) hi[c] = ww[c] >> Codec<BITS>::HI_SHIFT;
+    float wt[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float4 lo = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0);
+        const float4 up = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0 + 4);
+        wt[g][0] = lo.x; wt[g][1] = lo.y; wt[g][2] = lo.z; wt[g][3] = lo.w;
+        wt[g][4] = up.x; wt[g][5] = up.y; wt[g][6] = up.z; wt[g][7] = up.w;
+    }
+    static_for<8>([&](auto jc) {
+        constexpr int j = decltype(jc)::value;
+        if (!PARTIAL || J0 + j < count) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float q = code_f<BITS, J0 + j>(ww[c], hi[c]);
+                const float xh = replay_step<EXACT>(q, ch[c], smin, smax);
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc[g][c] = fmaf(wt[g][j], xh, acc[g][c]);
+            }
+        }
+    });
+}
+
+struct VArgs {
+    uint8_t *cache;         // [B, Hkv, n_super_cap, D] words
+    const __half *x_new;    // [B, Hkv, D]
+    __half *out;            // [B, Hq, D]
+    ParamPtrs p;
+    int Hq, Hkv, T, n_super_cap;
+    float smin, smax;
+};
+
+// Source interface (duck-typed):
+//   bool tile_weights(int i, int ntok, int lane, float (&acc)[G][4])
+//        fill wts[g][0..31] for tile i (0 for tokens >= ntok); may rescale acc (online softmax);
+//        false = bounded wait gave up
+//   bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
+//   float norm(int g)        final divisor (1 for pre-normalised weights)
+template <int BITS, int G, bool EXACT, class Src>
+__device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, uint8_t *ring_buf,
+                                       uint64_t *ring_bar, const float *wts, Src &src)
+{
+    using C = Codec<BITS>;
+    const int bh = b * a.Hkv + h;
+    Chan ch[4];
+    load_chan4<EXACT>(ch, a.p, h, 4 * lane);
+    float acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
+
+    uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
+    StreamRing<BITS> ring{ring_buf, ring_bar, stream, (a.T + kTileTok - 1) / kTileTok, a.T, kStatVWait};
+    ring.prologue(lane);
+
+    bool ok = true;
+    int i = 0;
+    for (; i < ring.n_tiles; ++i) {
+        const int ntok = min(kTileTok, a.T - i * kTileTok);
+        if (!(ok = src.tile_weights(i, ntok, lane, acc))) break;
+        if (!(ok = ring.wait(i))) break;
+        const uint4 *tile = ring.tile(i, lane);
+        if (ntok == kTileTok) {
+#pragma unroll
+            for (int wd = 0; wd < Tile<BITS>::WORDS; ++wd) {
+                const uint4 w = tile[wd * (kD / 4)];
+                v_chunk<BITS, G, EXACT, 0, false>(w, ch, wts, wd * C::TPW, acc, 8, a.smin, a.smax);
+                if (C::TPW == 16)
+                    v_chunk<BITS, G, EXACT, 8 % C::TPW, false>(w, ch, wts, wd * C::TPW + 8, acc, 8, a.smin, a.smax);
+            }
+        } else {
+            for (int wd = 0; wd * C::TPW < ntok; ++wd) {
+                const uint4 w = tile[wd * (kD / 4)];
+                const int count = ntok - wd * C::TPW;
+                v_chunk<BITS, G, EXACT, 0, true>(w, ch, wts, wd * C::TPW, acc, count, a.smin, a.smax);
+                if (C::TPW == 16 && count > 8)
+                    v_chunk<BITS, G, EXACT, 8 % C::TPW, true>(w, ch, wts, wd * C::TPW + 8, acc, count, a.smin,
+                                                              a.smax);
+            }
+        }
+        ring.release_and_refill(i, lane);   // also orders this tile's reads of wts before the next fill
+    }
+    if (!ok) {
+        ring.drain(i);
+        return;
+    }
+
+    float w_self[G];
+    if (!src.self_weight(lane, acc, w_self, a.T)) return;
+
+    float xn[4], xh[4];
+    load_half4(xn, a.x_new + size_t(bh) * kD + 4 * lane);
+    uint4 *slot = reinterpret_cast<uint4 *>(stream) + size_t(a.T / C::TPW) * (kD / 4) + lane;
+    uint4 wv = *slot;
+    uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    const int sh = BITS * (a.T % C::TPW);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        float rh;
+        const float q = quantize<BITS>(xn[c], ch[c], rh);
+        xh[c] = __fadd_rn(rh, ch[c].zp);
+        ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+    }
+    *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float inv = 1.0f / src.norm(g);
+        float o[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[c] = fmaf(w_self[g], xh[c], acc[g][c]) * inv;
+        store_half4(a.out + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane, o);
+    }
+}
+
+}  // namespace adkv

@@ -1,0 +1,252 @@
+// Device-side building blocks of the ADKV kernels (sm_100a): code extraction, the fp32
+// recurrence in its canonical and contracted forms, mbarrier / bulk-copy (1-D TMA) wrappers
+// with bounded waits.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <type_traits>
+#include <utility>
+
+namespace adkv {
+
+// Compile-time loop: f(std::integral_constant<int, 0>{}) ... f(std::integral_constant<int, N-1>{}).
+template <class F, int... I>
+__device__ __forceinline__ void static_for_impl(F &&f, std::integer_sequence<int, I...>)
+{
+    (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, class F>
+__device__ __forceinline__ void static_for(F &&f)
+{
+    static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
+
+constexpr int kD = 128;              // head dim served by this build
+constexpr float kEps = 1e-8f;        // src/adkv/train/train_model.py:9
+constexpr unsigned kFull = 0xffffffffu;
+
+// Status codes written to g_status when a bounded wait gives up.
+constexpr int kStatKWait = 1, kStatVWait = 2, kStatLFullWait = 3, kStatLEmptyWait = 4, kStatDrain = 5;
+
+// One status word per translation unit that includes this header (the library is one unit).
+static __device__ int g_status = 0;
+
+// ------------------------------------------------------------------------------------------
+// Codes.  Word (sg, c) holds TPW tokens of channel c, token j in bits [BITS*j, BITS*j+BITS)
+// as code + BIAS (4-bit layout: src/adkv/kernel/gemv.cu:266-305).
+template <int BITS>
+struct Codec {
+    static constexpr int TPW = 32 / BITS;
+    static constexpr int BIAS = 1 << (BITS - 1);
+    static constexpr uint32_t FIELD = (1u << BITS) - 1u;
+    static constexpr int DIRECT = 23 / BITS;   // fields that lie inside the fp32 mantissa in place
+    static constexpr int HI_SHIFT = 12;        // the remaining fields are taken from word >> 12
+    __host__ __device__ static constexpr float qlo() { return -float(BIAS); }
+    __host__ __device__ static constexpr float qhi() { return float(BIAS - 1); }
+};
+
+// Code of token J (compile time) as a float, without an integer-to-float conversion: the
+// field is masked in place into the mantissa of 2^(23-p) (p = bit position of the field), which
+// makes the float 2^(23-p) + field; subtracting 2^(23-p) + BIAS is exact.
+template <int BITS, int J>
+__device__ __forceinline__ float code_f(uint32_t w, uint32_t whi)
+{
+    using C = Codec<BITS>;
+    constexpr bool direct = J < C::DIRECT;
+    constexpr int P = BITS * (direct ? J : J - C::HI_SHIFT / BITS);
+    static_assert(P + BITS <= 23, "field must lie inside the mantissa");
+    constexpr uint32_t m = C::FIELD << P;
+    constexpr uint32_t e = uint32_t(127 + 23 - P) << 23;
+    const float f = __uint_as_float(((direct ? w : whi) & m) | e);
+    constexpr float c = float(1u << (23 - P)) + float(C::BIAS);
+    return __fsub_rn(f, c);
+}
+
+template <int BITS>
+__device__ __forceinline__ float code_f_rt(uint32_t w, int j)
+{
+    using C = Codec<BITS>;
+    return float(int((w >> (BITS * j)) & C::FIELD) - C::BIAS);
+}
+
+// ------------------------------------------------------------------------------------------
+// The recurrence (src/adkv/train/train_model.py:70-81).  tc = target (canonical) or
+// 1 - beta*target (contracted form).
+struct Chan {
+    float zp, s, alpha, beta, tc;
+};
+
+// Decoder side of one token: dequantise code q with the current state, then advance.
+template <bool EXACT>
+__device__ __forceinline__ float replay_step(float q, Chan &c, float smin, float smax)
+{
+    const float ss = fmaxf(c.s, kEps);
+    const float rh = __fmul_rn(q, ss);
+    const float xh = __fadd_rn(rh, c.zp);
+    if (EXACT) {
+        c.zp = __fadd_rn(c.zp, __fmul_rn(c.alpha, rh));
+        const float err = __fsub_rn(fabsf(q), c.tc);
+        c.s = fminf(fmaxf(__fadd_rn(c.s, __fmul_rn(__fmul_rn(c.s, c.beta), err)), smin), smax);
+    } else {
+        c.zp = fmaf(c.alpha, rh, c.zp);
+        const float g = fmaf(c.beta, fabsf(q), c.tc);
+        c.s = fminf(fmaxf(c.s * g, smin), smax);
+    }
+    return xh;
+}
+
+// Encoder side of one token, canonical order only (train_model.py:72, :8-17).  Returns the
+// code as a float; rh = q * max(s, eps).
+template <int BITS>
+__device__ __forceinline__ float quantize(float x, const Chan &c, float &rh)
+{
+    const float ss = fmaxf(c.s, kEps);
+    const float v = __fdiv_rn(__fsub_rn(x, c.zp), ss);
+    const float q = fminf(fmaxf(rintf(v), Codec<BITS>::qlo()), Codec<BITS>::qhi());
+    rh = __fmul_rn(q, ss);
+    return q;
+}
+
+__device__ __forceinline__ void advance_canonical(float q, float rh, Chan &c, float smin, float smax)
+{
+    c.zp = __fadd_rn(c.zp, __fmul_rn(c.alpha, rh));
+    const float err = __fsub_rn(fabsf(q), c.tc);
+    c.s = fminf(fmaxf(__fadd_rn(c.s, __fmul_rn(__fmul_rn(c.s, c.beta), err)), smin), smax);
+}
+
+// ------------------------------------------------------------------------------------------
+// mbarrier + bulk copy (non-multicast 1-D TMA) wrappers.
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init_fence()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Wait for a phase with a wall-clock limit (1 s).  Every lane of the calling warp must call it;
+// the result is warp-uniform.  On failure the status word records `code`.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int code)
+{
+    bool ok = mbar_try_wait(bar, parity);
+    if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        for (uint32_t it = 1;; ++it) {
+            ok = mbar_try_wait(bar, parity);
+            if (ok) break;
+            if ((it & 63u) == 0 && globaltimer_ns() - t0 > 1000000000ull) break;
+        }
+    }
+    ok = __all_sync(kFull, ok);
+    if (!ok && (threadIdx.x & 31) == 0) atomicExch(&g_status, code);
+    return ok;
+}
+
+// Global -> shared bulk copy completing on an mbarrier.  dst, src 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFull, v, o));
+    return v;
+}
+
+// Load the five fp16 parameters of 4 consecutive channels starting at `c0` of kv head `h`.
+struct ParamPtrs {
+    const __half *zp_init, *scale_init, *alpha, *beta, *target;
+};
+
+template <bool EXACT>
+__device__ __forceinline__ void load_chan4(Chan (&ch)[4], const ParamPtrs &p, int h, int c0)
+{
+    const size_t off = size_t(h) * kD + c0;
+    const uint2 a = *reinterpret_cast<const uint2 *>(p.zp_init + off);
+    const uint2 b = *reinterpret_cast<const uint2 *>(p.scale_init + off);
+    const uint2 c = *reinterpret_cast<const uint2 *>(p.alpha + off);
+    const uint2 d = *reinterpret_cast<const uint2 *>(p.beta + off);
+    const uint2 e = *reinterpret_cast<const uint2 *>(p.target + off);
+    const __half2 *pa = reinterpret_cast<const __half2 *>(&a), *pb = reinterpret_cast<const __half2 *>(&b),
+                  *pc = reinterpret_cast<const __half2 *>(&c), *pd = reinterpret_cast<const __half2 *>(&d),
+                  *pe = reinterpret_cast<const __half2 *>(&e);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float2 za = __half22float2(pa[i]), sb = __half22float2(pb[i]), al = __half22float2(pc[i]),
+                     be = __half22float2(pd[i]), tg = __half22float2(pe[i]);
+        ch[2 * i] = Chan{za.x, sb.x, al.x, be.x, EXACT ? tg.x : fmaf(-be.x, tg.x, 1.0f)};
+        ch[2 * i + 1] = Chan{za.y, sb.y, al.y, be.y, EXACT ? tg.y : fmaf(-be.y, tg.y, 1.0f)};
+    }
+}
+
+__device__ __forceinline__ void load_half4(float (&v)[4], const __half *p)
+{
+    const uint2 a = *reinterpret_cast<const uint2 *>(p);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&a.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&a.y));
+    v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+}
+
+__device__ __forceinline__ void store_half4(__half *p, const float (&v)[4])
+{
+    const __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
+    uint2 a;
+    a.x = *reinterpret_cast<const uint32_t *>(&lo);
+    a.y = *reinterpret_cast<const uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = a;
+}
+
+}  // namespace adkv

@@ -1,0 +1,228 @@
+"""Host-side mirror of the reference's kernel module ``adkv.kernel.gemv``.
+
+``encode_kv``, ``forward_qk`` and ``forward_ov`` keep the reference's names, positional
+arguments, in-place semantics and error behaviour (``src/adkv/kernel/gemv.py:16-132``; argument
+checks of ``src/adkv/kernel/gemv.cu:375-398, 892-912, 1241-1266``), so the reference's model file
+``src/adkv/hf/llama_adkv.py`` runs on top of this module unchanged (see ``adkv_b200.hf_shim``).
+They call hand-written sm_100a kernels through the C ABI of ``libadkv_b200.so`` on the current
+torch CUDA stream.  Keyword-only extensions: ``bits`` (4 or 2), ``fast`` (contracted replay),
+grouped-query heads (``q`` may have a multiple of the cache's heads).
+
+``decode_attn`` is the fused decode step (q.K^T, scaling, mask, softmax, P.V and both appends in one
+launch) that replaces the three-call sequence of ``src/adkv/hf/llama_adkv.py:263-276``.
+``append_kv`` appends one token from a persisted tail state without replaying the cache.
+
+Arithmetic is the reference's fp32 torch/Triton recurrence
+(``src/adkv/train/train_model.py:70-81``), not the fp16 arithmetic of the reference's CUDA file;
+``scale_min`` / ``scale_max`` are honoured.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+__all__ = ["encode_kv", "forward_qk", "forward_ov", "decode_attn", "append_kv", "n_super_for"]
+
+
+def n_super_for(tokens: int, bits: int = 4) -> int:
+    """Supergroups (words per channel) that hold ``tokens`` tokens."""
+    tpw = 32 // bits
+    return (tokens + tpw - 1) // tpw
+
+
+def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _params(names, tensors, H, D, device):
+    for n, t in zip(names, tensors):
+        _require(t.dtype == torch.float16, f"{n} must be float16")
+        _require(t.is_cuda and t.device == device, f"{n} must be on the cache's CUDA device")
+        _require(t.numel() == H * D, f"{n} must have {H} x {D} elements")
+    keep = [t.contiguous() for t in tensors]
+    return _lib.Params(*[t.data_ptr() for t in keep]), keep
+
+
+def _cache_dims(cache: torch.Tensor, name: str):
+    _require(cache.dtype == torch.uint8, f"{name} must be uint8")
+    _require(cache.is_cuda, f"{name} must be a CUDA tensor (adkv_b200 has no CPU path)")
+    _require(cache.dim() == 6 and cache.shape[4] == 4 and cache.shape[5] == 4,
+             f"{name} must be [B, nh, n_super_cap, DIM/4, 4, 4]")
+    return cache.shape[0], cache.shape[1], cache.shape[2], cache.shape[3] * 4
+
+
+def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min, scale_max, *,
+              bits: int = 4, tail: torch.Tensor | None = None, t_start: int = 0):
+    """Prefill: quantise tokens ``[t_start, t_start+T)`` into the packed cache, in place.
+
+    Same contract as the reference's ``encode_kv`` (``src/adkv/kernel/gemv.py:100-132``) for
+    ``t_start == 0``.  ``tail`` (float32 ``[B, nh, 2, DIM]``) optionally receives the state after the
+    last token and, for ``t_start > 0``, supplies the state to continue from.  Returns ``kv_cache``."""
+    _require(kv_new.dtype == torch.float16, "kv_new must be float16")
+    B, H, n_super_cap, D = _cache_dims(kv_cache, "kv_cache")
+    _require(kv_cache.is_contiguous(), "kv_cache must be contiguous (written in place)")
+    _require(kv_new.dim() == 4, "kv_new must be [B, nh, T, DIM]")
+    _require(kv_new.shape[3] == D, "kv_cache channel groups do not match kv_new head dim")
+    _require(kv_new.shape[0] == B and kv_new.shape[1] == H, "kv_new batch/heads do not match kv_cache")
+    T = kv_new.shape[2]
+    need = n_super_for(t_start + T, bits)
+    _require(need <= n_super_cap,
+             f"kv_cache capacity too small: need {need} supergroups for {t_start + T} tokens, have {n_super_cap}")
+    p, keep = _params(("kv_zp", "kv_sc", "kv_alpha", "kv_beta", "kv_t"),
+                      (kv_zp, kv_sc, kv_alpha, kv_beta, kv_t), H, D, kv_cache.device)
+    x = kv_new.contiguous()
+    if tail is not None:
+        _require(tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape == (B, H, 2, D),
+                 "tail must be contiguous float32 [B, nh, 2, DIM]")
+    with torch.cuda.device(kv_cache.device):
+        rc = _lib.load().adkv_encode(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
+                                     None if tail is None else tail.data_ptr(), B, H, T, D, n_super_cap, bits,
+                                     t_start, scale_min, scale_max, _stream(kv_cache))
+    _lib.check(rc, "encode_kv")
+    return kv_cache
+
+
+def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min, scale_max, *, bits: int = 4):
+    """Quantise ``x_new [B, nh, 1, DIM]`` with the persisted ``tail`` state (after token ``T-1``),
+    write it as token ``T`` and advance ``tail`` in place.  Returns ``cache``."""
+    B, H, n_super_cap, D = _cache_dims(cache, "cache")
+    _require(cache.is_contiguous(), "cache must be contiguous (appended in place)")
+    _require(x_new.dtype == torch.float16, "x_new must be float16")
+    _require(x_new.numel() == B * H * D, "x_new must be [B, nh, 1, DIM]")
+    _require(T >= 0, "T must be non-negative")
+    _require(T // (32 // bits) < n_super_cap, f"cache has no free supergroup to append token {T}")
+    _require(tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape == (B, H, 2, D),
+             "tail must be contiguous float32 [B, nh, 2, DIM]")
+    p, keep = _params(("zp", "sc", "alpha", "beta", "target"), (zp, sc, alpha, beta, target), H, D, cache.device)
+    x = x_new.contiguous()
+    with torch.cuda.device(cache.device):
+        rc = _lib.load().adkv_append(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
+                                     B, H, T, D, n_super_cap, bits, scale_min, scale_max, _stream(cache))
+    _lib.check(rc, "append_kv")
+    return cache
+
+
+def forward_qk(q, k_cache, k_new, k_zp, k_sc, k_alpha, k_beta, k_t, T: int, scale_min, scale_max, *,
+               bits: int = 4, fast: bool = False):
+    """Decode-phase q.K^T over the packed cache; appends ``k_new`` as token ``T`` in place.
+
+    Same contract as the reference's ``forward_qk`` (``src/adkv/kernel/gemv.py:16-55``): returns
+    ``[B, nh_q, T + 1]`` float16 unscaled logits whose last entry is the logit of the appended token
+    computed from its dequantised code."""
+    _require(q.dtype == torch.float16, "q must be float16")
+    _require(k_new.dtype == torch.float16, "k_new must be float16")
+    B, Hkv, n_super_cap, D = _cache_dims(k_cache, "k_cache")
+    _require(k_cache.is_contiguous(), "k_cache must be contiguous (appended in place)")
+    _require(q.dim() == 4 and q.shape[2] == 1, "q must be [B, nh, 1, DIM]")
+    _require(D == q.shape[3], "q head dimension does not match k_cache")
+    _require(q.shape[0] == B, "q batch does not match k_cache")
+    Hq = q.shape[1]
+    _require(Hq % Hkv == 0, "q heads must be a multiple of the cache's heads")
+    _require(k_new.numel() == B * Hkv * D, "k_new must be [B, nh, 1, DIM]")
+    _require(T >= 0, "T must be non-negative")
+    _require(T // (32 // bits) < n_super_cap, f"k_cache has no free supergroup to append token {T}")
+    p, keep = _params(("k_zp", "k_sc", "k_alpha", "k_beta", "k_t"), (k_zp, k_sc, k_alpha, k_beta, k_t),
+                      Hkv, D, k_cache.device)
+    qc, kn = q.contiguous(), k_new.contiguous()
+    o = torch.empty((B, Hq, T + 1), dtype=torch.float16, device=k_cache.device)
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().adkv_forward_qk(qc.data_ptr(), k_cache.data_ptr(), kn.data_ptr(), ctypes.addressof(p),
+                                         o.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scale_min, scale_max,
+                                         _lib.FLAG_FAST_REPLAY if fast else 0, _stream(k_cache))
+    _lib.check(rc, "forward_qk")
+    return o
+
+
+def forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min, scale_max, *,
+               bits: int = 4, fast: bool = False):
+    """Decode-phase P.V over the packed cache; appends ``v_new`` as token ``T = attn.shape[2] - 1``.
+
+    Same contract as the reference's ``forward_ov`` (``src/adkv/kernel/gemv.py:58-97``): returns
+    ``[B, nh_q, DIM]`` float16; the last weight multiplies the dequantised appended token."""
+    _require(attn.dtype == torch.float16, "attn must be float16")
+    _require(v_new.dtype == torch.float16, "v_new must be float16")
+    B, Hkv, n_super_cap, D = _cache_dims(v_cache, "v_cache")
+    _require(v_cache.is_contiguous(), "v_cache must be contiguous (appended in place)")
+    _require(attn.dim() == 3 and attn.shape[0] == B, "attn must be [B, nh, T + 1]")
+    _require(attn.shape[2] >= 1, "attn must contain the cached weights plus the self weight")
+    Hq = attn.shape[1]
+    _require(Hq % Hkv == 0, "attn heads must be a multiple of the cache's heads")
+    T = attn.shape[2] - 1
+    _require(D == v_new.shape[-1], "v_new head dimension does not match v_cache")
+    _require(v_new.numel() == B * Hkv * D, "v_new must be [B, nh, 1, DIM]")
+    _require(T // (32 // bits) < n_super_cap, f"v_cache has no free supergroup to append token {T}")
+    p, keep = _params(("v_zp", "v_sc", "v_alpha", "v_beta", "v_t"), (v_zp, v_sc, v_alpha, v_beta, v_t),
+                      Hkv, D, v_cache.device)
+    ac, vn = attn.contiguous(), v_new.contiguous()
+    o = torch.empty((B, Hq, D), dtype=torch.float16, device=v_cache.device)
+    with torch.cuda.device(v_cache.device):
+        rc = _lib.load().adkv_forward_ov(ac.data_ptr(), v_cache.data_ptr(), vn.data_ptr(), ctypes.addressof(p),
+                                         o.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scale_min, scale_max,
+                                         _lib.FLAG_FAST_REPLAY if fast else 0, _stream(v_cache))
+    _lib.check(rc, "forward_ov")
+    return o
+
+
+def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
+                scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False,
+                out: torch.Tensor | None = None):
+    """Fused decode step over both packed caches.
+
+    ``q [B, nh_q, 1, DIM]``, ``k_new`` / ``v_new [B, nh_kv, 1, DIM]`` float16; ``k_params`` / ``v_params``
+    the five ``[nh_kv, DIM]`` float16 tensors (zp_init, scale_init, alpha, beta, target); ``mask`` an
+    additive ``[B, T+1]`` (or ``[B, 1, T+1]`` / ``[B, 1, 1, T+1]``) tensor shared by all heads.  Appends to
+    both caches in place as token ``T`` and returns ``softmax(q.K^T * scaling + mask) . V`` as
+    ``[B, nh_q, DIM]`` float16, the appended token included (``src/adkv/hf/llama_adkv.py:263-276``)."""
+    _require(q.dtype == torch.float16, "q must be float16")
+    _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "k_new / v_new must be float16")
+    B, Hkv, n_super_cap, D = _cache_dims(k_cache, "k_cache")
+    _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
+             "v_cache must match k_cache")
+    _require(k_cache.is_contiguous() and v_cache.is_contiguous(), "caches must be contiguous (appended in place)")
+    _require(q.dim() == 4 and q.shape[2] == 1 and q.shape[0] == B and q.shape[3] == D, "q must be [B, nh, 1, DIM]")
+    Hq = q.shape[1]
+    _require(Hq % Hkv == 0, "q heads must be a multiple of the cache's heads")
+    _require(k_new.numel() == B * Hkv * D and v_new.numel() == B * Hkv * D, "k_new / v_new must be [B, nh, 1, DIM]")
+    _require(T >= 0, "T must be non-negative")
+    _require(T // (32 // bits) < n_super_cap, f"cache has no free supergroup to append token {T}")
+    names = ("zp", "sc", "alpha", "beta", "t")
+    kp, keep_k = _params(tuple("k_" + n for n in names), tuple(k_params), Hkv, D, k_cache.device)
+    vp, keep_v = _params(tuple("v_" + n for n in names), tuple(v_params), Hkv, D, k_cache.device)
+    qc, kn, vn = q.contiguous(), k_new.contiguous(), v_new.contiguous()
+    mptr, mstride, mk = None, 0, None
+    if mask is not None:
+        _require(mask.shape[0] == B and mask.shape[-1] == T + 1 and mask.numel() == B * (T + 1),
+                 "mask must be [B, T + 1], shared by all heads")
+        mk = mask.reshape(B, T + 1).to(device=k_cache.device, dtype=torch.float32).contiguous()
+        mptr, mstride = mk.data_ptr(), T + 1
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.float16, device=k_cache.device)
+    else:
+        _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
+                 "out must be contiguous float16 [B, nh_q, DIM]")
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().adkv_decode_attn(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
+                                          vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp), mptr, mstride,
+                                          out.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scaling,
+                                          scale_min, scale_max, _lib.FLAG_FAST_REPLAY if fast else 0,
+                                          _stream(k_cache))
+    _lib.check(rc, "decode_attn")
+    return out
+
+
+def device_status(device=None) -> int:
+    """Read and clear the device status word (non-zero: a kernel gave up on a bounded wait)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    val = ctypes.c_int(0)
+    with torch.cuda.device(dev):
+        rc = _lib.load().adkv_device_status(ctypes.byref(val), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _lib.check(rc, "device_status")
+    return val.value

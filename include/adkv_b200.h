@@ -1,0 +1,114 @@
+/* adkv_b200 -- C ABI of the B200 (sm_100a) ADKV hot path.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless stated, every
+ * call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream) and performs no host synchronisation and no allocation.  The library
+ * never keeps a pointer across calls: the caller owns and may replace the caches between
+ * calls (the reference's cache object reallocates them as they grow,
+ * src/adkv/hf/llama_adkv.py:104-123).
+ *
+ * Return value: 0 on success, < 0 for an argument error (ADKV_E_*), > 0 for a CUDA runtime
+ * error code (cudaError_t) raised by the launch.  adkv_strerror() gives text for both.
+ *
+ * Packed cache layout (src/adkv/kernel/gemv.cu:502-510 for 4 bits): per (batch, kv head) a
+ * row-major array uint32[n_super_cap][D]; word (sg, c) holds the codes of channel c for the
+ * tokens of supergroup sg, token j of the supergroup in bits [bits*j, bits*j+bits) stored as
+ * code - lower_limit (4-bit: q + 8, 8 tokens per word; 2-bit: q + 2, 16 tokens per word --
+ * the 2-bit layout has no counterpart in the reference).  As a uint8 tensor this is the
+ * reference's [B, H, n_super_cap, D/4, 4, 4] tile.
+ *
+ * Arithmetic: the fp32 recurrence of src/adkv/train/train_model.py:6-22, 70-81 (the
+ * reference's torch/Triton definition), evaluated with one rounding per operation in that
+ * order ("canonical").  ADKV_FLAG_FAST_REPLAY lets the decode kernels replay the cached
+ * tokens with fused multiply-adds instead (see DESIGN notes in the repository): attention
+ * outputs stay within tolerance, and an appended code may differ from the canonical one by
+ * one step in rare cases.
+ */
+#ifndef ADKV_B200_H
+#define ADKV_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ADKV_ABI_VERSION 1
+
+/* argument errors */
+#define ADKV_E_NULL      (-1)  /* a required pointer is NULL */
+#define ADKV_E_HEAD_DIM  (-2)  /* D is not supported (this build: 128) */
+#define ADKV_E_BITS      (-3)  /* bits is not 2 or 4 */
+#define ADKV_E_SHAPE     (-4)  /* negative size, or Hq not a multiple of Hkv, or group size unsupported */
+#define ADKV_E_CAPACITY  (-5)  /* the cache has no room for the tokens to be written */
+#define ADKV_E_ALIGN     (-6)  /* a pointer is not 16-byte aligned */
+#define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
+
+/* flags */
+#define ADKV_FLAG_FAST_REPLAY 1u  /* decode kernels: contracted (FMA) replay of cached tokens */
+
+/* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each
+ * (src/adkv/hf/llama_adkv.py:27: zp_init, scale_init, alpha, beta, quant_target). */
+typedef struct adkv_params {
+    const void *zp_init;
+    const void *scale_init;
+    const void *alpha;
+    const void *beta;
+    const void *target;
+} adkv_params;
+
+int adkv_abi_version(void);
+const char *adkv_strerror(int code);
+
+/* Prefill quantise + pack.  Replaces encode_kv (src/adkv/kernel/gemv.cu:368-414, called from
+ * src/adkv/hf/llama_adkv.py:144-153).
+ *   cache  uint32 [B, H, n_super_cap, D]   written for tokens [t_start, t_start+T)
+ *   x      fp16   [B, H, T, D]
+ *   tail   float  [B, H, 2, D] (zp then scale) or NULL.  When given it receives the state after
+ *          the last token; with t_start > 0 it must hold the state after token t_start-1 on
+ *          entry (chunked prefill, which the reference cannot do: llama_adkv.py:195-197).
+ * With t_start == 0 the recurrence starts from (zp_init, scale_init) and the unused fields of
+ * the last written word are zeroed (gemv.cu:243, 300-305). */
+int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail,
+                int B, int H, int T, int D, int n_super_cap, int bits, int t_start,
+                float scale_min, float scale_max, void *stream);
+
+/* Single-token append from a persisted tail state (no replay).  No direct counterpart in the
+ * reference, whose append happens inside forward_qk/forward_ov after a full replay
+ * (src/adkv/kernel/gemv.cu:91-146, 744-764); same arithmetic, same slot.
+ *   x_new fp16 [B, H, D]; tail float [B, H, 2, D] in/out; T = index of the token written. */
+int adkv_append(void *cache, const void *x_new, const adkv_params *p, void *tail,
+                int B, int H, int T, int D, int n_super_cap, int bits,
+                float scale_min, float scale_max, void *stream);
+
+/* q.K^T over the packed cache + append of k_new as token T + self logit.  Replaces forward_qk
+ * (src/adkv/kernel/gemv.cu:883-939, called from src/adkv/hf/llama_adkv.py:264).
+ *   q fp16 [B, Hq, D]; k_cache [B, Hkv, n_super_cap, D] words; k_new fp16 [B, Hkv, D];
+ *   logits fp16 [B, Hq, T+1] (unscaled, unmasked; entry T is the dequantised new token's). */
+int adkv_forward_qk(const void *q, void *k_cache, const void *k_new, const adkv_params *p, void *logits,
+                    int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
+                    float scale_min, float scale_max, unsigned flags, void *stream);
+
+/* P.V over the packed cache + append of v_new as token T + self term.  Replaces forward_ov
+ * (src/adkv/kernel/gemv.cu:1233-1288, called from src/adkv/hf/llama_adkv.py:273).
+ *   attn fp16 [B, Hq, T+1]; v_cache words; v_new fp16 [B, Hkv, D]; out fp16 [B, Hq, D]. */
+int adkv_forward_ov(const void *attn, void *v_cache, const void *v_new, const adkv_params *p, void *out,
+                    int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
+                    float scale_min, float scale_max, unsigned flags, void *stream);
+
+/* Fused decode step: q.K^T, * scaling, + mask, softmax, P.V, both appends, one launch.  Replaces the
+ * sequence forward_qk -> torch softmax -> forward_ov of src/adkv/hf/llama_adkv.py:263-276.
+ *   mask float [B, T+1] additive, shared by all heads (row stride mask_stride_b elements), or NULL.
+ *   out  fp16 [B, Hq, D]. */
+int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                     const adkv_params *kp, const adkv_params *vp, const void *mask, long long mask_stride_b,
+                     void *out, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
+                     float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
+
+/* Reads and clears the device-side status word of the current device (HOST pointer `status`;
+ * synchronises `stream`).  Non-zero means a kernel gave up on a bounded wait; the value encodes
+ * which wait.  Intended for tests and diagnostics, not for the hot path. */
+int adkv_device_status(int *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADKV_B200_H */

@@ -1,0 +1,274 @@
+"""Parity of the CUDA path (called through the C ABI) against the oracle.  Needs a B200."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from adkv_b200 import gemv, synth
+from oracle import adkv_oracle as orc
+from tests.util import SMAX, SMIN, code_mismatch, dev, make_case, np_params, oracle_prefill
+
+pytestmark = pytest.mark.gpu
+
+# north_star tolerance for fp16 attention outputs
+RTOL, ATOL = 2e-3, 2e-3
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+
+
+def _status_ok():
+    assert gemv.device_status() == 0, "a kernel gave up on a bounded wait"
+
+
+# ------------------------------------------------------------------------------- encode
+
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("T", [1, 7, 8, 9, 16, 17, 77, 130])
+def test_encode_bit_exact(bits, T):
+    B, H, D = 2, 3, 128
+    x = synth.gen_kv(11 + T, B, H, T, D)
+    p = synth.gen_params(12, H, D, bits)
+    ns = orc.n_super_for(T, bits) + 1
+    want = np.zeros(orc.cache_shape(B, H, ns, D), np.uint8)
+    _, st = orc.encode_kv(want, x.numpy(), np_params(p), bits, SMIN, SMAX)
+    cache = torch.full(want.shape, 0xAB, dtype=torch.uint8, device="cuda")   # stale bytes must be overwritten
+    tail = torch.empty(B, H, 2, D, dtype=torch.float32, device="cuda")
+    out = gemv.encode_kv(cache, dev(x), *dev(p), SMIN, SMAX, bits=bits, tail=tail)
+    assert out is cache
+    used = orc.n_super_for(T, bits)
+    assert np.array_equal(cache.cpu().numpy()[:, :, :used], want[:, :, :used])
+    assert np.all(cache.cpu().numpy()[:, :, used:] == 0xAB)          # untouched beyond the last word
+    t = tail.cpu().numpy()
+    assert np.array_equal(t[:, :, 0].view(np.uint32), st.zp.view(np.uint32))
+    assert np.array_equal(t[:, :, 1].view(np.uint32), st.s.view(np.uint32))
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_encode_reproduces_reference_fixtures(path):
+    """Codes written by the kernel equal the codes the reference's torch code produced."""
+    d = np.load(path)
+    bits = int(d["bits"])
+    names = ("zp_init", "scale_init", "alpha", "beta", "target")
+    p16 = tuple(torch.from_numpy(d[k]).half() for k in names)
+    if any(not torch.equal(a.float(), torch.from_numpy(d[k])) for a, k in zip(p16, names)):
+        pytest.skip("fixture parameters are not fp16-representable (the kernel API takes fp16 parameters)")
+    x = torch.from_numpy(d["x"])
+    B, H, T, D = x.shape
+    cache = torch.zeros(orc.cache_shape(B, H, orc.n_super_for(T, bits), D), dtype=torch.uint8, device="cuda")
+    tail = torch.empty(B, H, 2, D, dtype=torch.float32, device="cuda")
+    gemv.encode_kv(cache, dev(x), *dev(p16), float(d["scale_min"]), float(d["scale_max"]), bits=bits, tail=tail)
+    got = orc.unpack_codes(cache.cpu().numpy(), T, bits)
+    assert np.array_equal(got, d["codes"])
+    assert np.array_equal(tail.cpu().numpy()[:, :, 1].view(np.uint32), d["s_final"].view(np.uint32))
+    assert np.array_equal(tail.cpu().numpy()[:, :, 0].view(np.uint32), d["zp_final"].view(np.uint32))
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_chunked_encode_and_append_equal_one_shot(bits):
+    B, H, D, T = 2, 2, 128, 61
+    x = synth.gen_kv(21, B, H, T, D)
+    p = dev(synth.gen_params(22, H, D, bits))
+    ns = orc.n_super_for(T, bits)
+    full = torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    tail_full = torch.empty(B, H, 2, D, dtype=torch.float32, device="cuda")
+    gemv.encode_kv(full, dev(x), *p, SMIN, SMAX, bits=bits, tail=tail_full)
+    part = torch.zeros_like(full)
+    tail = torch.empty_like(tail_full)
+    gemv.encode_kv(part, dev(x[:, :, :19]), *p, SMIN, SMAX, bits=bits, tail=tail)
+    gemv.encode_kv(part, dev(x[:, :, 19:50]), *p, SMIN, SMAX, bits=bits, tail=tail, t_start=19)
+    for t in range(50, T):
+        gemv.append_kv(part, dev(x[:, :, t:t + 1]), *p, tail, t, SMIN, SMAX, bits=bits)
+    assert torch.equal(full, part)
+    assert torch.equal(tail_full.view(torch.int32), tail.view(torch.int32))
+
+
+# ------------------------------------------------------------------------------- decode
+
+CASES = [
+    # B, Hq, Hkv, T, bits
+    (2, 2, 2, 0, 4), (2, 2, 2, 1, 4), (1, 3, 3, 31, 4), (2, 2, 2, 32, 4), (2, 2, 2, 33, 4), (1, 2, 2, 64, 4),
+    (2, 4, 4, 205, 4), (1, 2, 2, 1031, 4),
+    (2, 2, 2, 0, 2), (1, 2, 2, 15, 2), (2, 2, 2, 16, 2), (1, 2, 2, 47, 2), (2, 3, 3, 200, 2),
+    (2, 4, 2, 77, 4), (1, 8, 2, 130, 2), (1, 8, 1, 40, 4),
+]
+
+
+@pytest.mark.parametrize("fast", [False, True], ids=["exact", "fast"])
+@pytest.mark.parametrize("B,Hq,Hkv,T,bits", CASES)
+def test_forward_qk(B, Hq, Hkv, T, bits, fast):
+    case = make_case(100 + T, B, Hq, Hkv, T, bits, random_params=(T % 2 == 1))
+    kc, _ = oracle_prefill(case)
+    want_cache = kc.copy()
+    want = orc.forward_qk(case["q"][:, :, 0].numpy(), want_cache, case["k"][:, :, T].numpy(),
+                          np_params(case["kp"]), T, bits, SMIN, SMAX)
+    cache = dev(kc)
+    got = gemv.forward_qk(dev(case["q"]), cache, dev(case["k"][:, :, T:T + 1]), *dev(case["kp"]), T, SMIN, SMAX,
+                          bits=bits, fast=fast)
+    _status_ok()
+    assert got.shape == (B, Hq, T + 1) and got.dtype == torch.float16
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    if not fast:
+        assert np.array_equal(cache.cpu().numpy(), want_cache)          # appended code bit-exact
+    else:
+        frac, dmax = code_mismatch(cache.cpu().numpy(), want_cache, T + 1, bits)
+        assert dmax <= 1 and frac <= 1e-4 + 2.0 / (B * Hkv * 128 * (T + 1))
+
+
+@pytest.mark.parametrize("fast", [False, True], ids=["exact", "fast"])
+@pytest.mark.parametrize("B,Hq,Hkv,T,bits", CASES)
+def test_forward_ov(B, Hq, Hkv, T, bits, fast):
+    case = make_case(200 + T, B, Hq, Hkv, T, bits, random_params=(T % 2 == 1))
+    _, vc = oracle_prefill(case)
+    g = torch.Generator().manual_seed(T)
+    attn = torch.softmax(torch.randn(B, Hq, T + 1, generator=g) * 2, dim=-1).half()
+    want_cache = vc.copy()
+    want = orc.forward_ov(attn.float().numpy(), want_cache, case["v"][:, :, T].numpy(), np_params(case["vp"]),
+                          bits, SMIN, SMAX)
+    cache = dev(vc)
+    got = gemv.forward_ov(dev(attn), cache, dev(case["v"][:, :, T:T + 1]), *dev(case["vp"]), SMIN, SMAX,
+                          bits=bits, fast=fast)
+    _status_ok()
+    assert got.shape == (B, Hq, 128) and got.dtype == torch.float16
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    if not fast:
+        assert np.array_equal(cache.cpu().numpy(), want_cache)
+    else:
+        frac, dmax = code_mismatch(cache.cpu().numpy(), want_cache, T + 1, bits)
+        assert dmax <= 1 and frac <= 1e-4 + 2.0 / (B * Hkv * 128 * (T + 1))
+
+
+@pytest.mark.parametrize("fast", [False, True], ids=["exact", "fast"])
+@pytest.mark.parametrize("with_mask", [False, True], ids=["nomask", "mask"])
+@pytest.mark.parametrize("B,Hq,Hkv,T,bits", CASES)
+def test_decode_attn(B, Hq, Hkv, T, bits, with_mask, fast):
+    case = make_case(300 + T, B, Hq, Hkv, T, bits, outlier_mode="persistent" if T % 3 == 0 else "scale")
+    kc, vc = oracle_prefill(case)
+    mask = None
+    if with_mask:
+        mask = torch.zeros(B, 1, 1, T + 1)
+        mask[0, ..., : (T + 1) // 3] = torch.finfo(torch.float16).min      # HF-style additive mask (left padding)
+        mask[-1, ..., T // 2] = -3.0
+    scaling = 128 ** -0.5
+    wk, wv = kc.copy(), vc.copy()
+    want = orc.decode_attn(case["q"][:, :, 0].numpy(), wk, wv, case["k"][:, :, T].numpy(), case["v"][:, :, T].numpy(),
+                           np_params(case["kp"]), np_params(case["vp"]), T, scaling,
+                           mask=None if mask is None else mask[:, 0].numpy(), bits=bits,
+                           scale_min=SMIN, scale_max=SMAX)
+    dk, dv = dev(kc), dev(vc)
+    got = gemv.decode_attn(dev(case["q"]), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
+                           dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX,
+                           mask=None if mask is None else dev(mask), bits=bits, fast=fast)
+    _status_ok()
+    assert got.shape == (B, Hq, 128) and got.dtype == torch.float16
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    if not fast:
+        assert np.array_equal(dk.cpu().numpy(), wk) and np.array_equal(dv.cpu().numpy(), wv)
+
+
+def test_decode_steps_chain_like_generation():
+    """Prefill with the kernel, then 40 fused decode steps; caches stay bit-identical to the oracle's."""
+    B, H, T0, steps, bits, D = 2, 2, 21, 40, 4, 128
+    case = make_case(7, B, H, H, T0 + steps, bits)
+    kp, vp = dev(case["kp"]), dev(case["vp"])
+    ns = orc.n_super_for(T0 + steps + 1, bits)
+    dk = torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    dv = torch.zeros_like(dk)
+    gemv.encode_kv(dk, dev(case["k"][:, :, :T0]), *kp, SMIN, SMAX)
+    gemv.encode_kv(dv, dev(case["v"][:, :, :T0]), *vp, SMIN, SMAX)
+    ok_, ov_ = dk.cpu().numpy().copy(), dv.cpu().numpy().copy()
+    g = torch.Generator().manual_seed(3)
+    for s in range(steps):
+        T = T0 + s
+        q = torch.randn(B, H, 1, D, generator=g).half()
+        want = orc.decode_attn(q[:, :, 0].numpy(), ok_, ov_, case["k"][:, :, T].numpy(), case["v"][:, :, T].numpy(),
+                               np_params(case["kp"]), np_params(case["vp"]), T, 0.1, bits=bits,
+                               scale_min=SMIN, scale_max=SMAX)
+        got = gemv.decode_attn(dev(q), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
+                               kp, vp, T, 0.1, SMIN, SMAX, bits=bits)
+        np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    _status_ok()
+    assert np.array_equal(dk.cpu().numpy(), ok_) and np.array_equal(dv.cpu().numpy(), ov_)
+
+
+def test_unfused_trio_matches_fused():
+    """forward_qk -> torch softmax -> forward_ov (the reference caller's sequence) vs the fused kernel."""
+    case = make_case(55, 2, 4, 4, 300, 4)
+    kc, vc = oracle_prefill(case)
+    T, scaling = 300, 128 ** -0.5
+    a_k, a_v, b_k, b_v = dev(kc), dev(vc), dev(kc), dev(vc)
+    q, kn, vn = dev(case["q"]), dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1])
+    logits = gemv.forward_qk(q, a_k, kn, *dev(case["kp"]), T, SMIN, SMAX)
+    w = torch.softmax(logits.float() * scaling, dim=-1).to(torch.float16)
+    o1 = gemv.forward_ov(w, a_v, vn, *dev(case["vp"]), SMIN, SMAX)
+    o2 = gemv.decode_attn(q, b_k, b_v, kn, vn, dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX)
+    assert torch.equal(a_k, b_k) and torch.equal(a_v, b_v)
+    torch.testing.assert_close(o1.float(), o2.float(), rtol=4e-3, atol=4e-3 * float(o2.abs().max()))
+
+
+def test_full_size_config2_properties():
+    """BASELINE config 2 shape (B 128, H 32, T 4096, 4-bit): the batch is 2 distinct sequences replicated 64
+    times, so every replica must reproduce the oracle's result for its sequence, and the appended slot must
+    equal the oracle's.  Also checks that re-running the step with the same T overwrites the same slot."""
+    B, H, T, bits, D, R = 128, 32, 4096, 4, 128, 2
+    case = make_case(900, R, H, H, T, bits)
+    from oracle import c_oracle
+    ns = orc.n_super_for(T + 1, bits)
+    kc = np.zeros(orc.cache_shape(R, H, ns, D), np.uint8)
+    vc = np.zeros_like(kc)
+    c_oracle.encode(kc, case["k"][:, :, :T].numpy(), np_params(case["kp"]), bits, SMIN, SMAX)
+    c_oracle.encode(vc, case["v"][:, :, :T].numpy(), np_params(case["vp"]), bits, SMIN, SMAX)
+    # the kernel's own prefill must give the same caches
+    dk = torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    dv = torch.zeros_like(dk)
+    rep = lambda t: dev(t).repeat(B // R, *([1] * (t.dim() - 1)))
+    gemv.encode_kv(dk, rep(case["k"][:, :, :T]), *dev(case["kp"]), SMIN, SMAX)
+    gemv.encode_kv(dv, rep(case["v"][:, :, :T]), *dev(case["vp"]), SMIN, SMAX)
+    assert np.array_equal(dk[:R].cpu().numpy(), kc) and torch.equal(dk[:R], dk[-R:])
+    assert np.array_equal(dv[:R].cpu().numpy(), vc)
+    scaling = D ** -0.5
+    want = c_oracle.decode_attn(case["q"][:, :, 0].numpy(), kc, vc, case["k"][:, :, T].numpy(),
+                                case["v"][:, :, T].numpy(), np_params(case["kp"]), np_params(case["vp"]),
+                                T, scaling, bits, SMIN, SMAX)
+    for fast in (False, True):
+        out = gemv.decode_attn(rep(case["q"]), dk, dv, rep(case["k"][:, :, T:T + 1]), rep(case["v"][:, :, T:T + 1]),
+                               dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, fast=fast)
+        _status_ok()
+        got = out.float().cpu().numpy().reshape(B // R, R, H, D)
+        assert np.array_equal(got, np.broadcast_to(got[0], got.shape))        # replicas agree bit for bit
+        np.testing.assert_allclose(got[0], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+        if not fast:
+            assert np.array_equal(dk[:R].cpu().numpy(), kc) and np.array_equal(dv[-R:].cpu().numpy(), vc)
+        else:
+            frac, dmax = code_mismatch(dk[:R].cpu().numpy(), kc, T + 1, bits)
+            assert dmax <= 1 and frac <= 1e-4
+
+
+# ------------------------------------------------------------------------------- errors
+
+def test_argument_errors_raise_runtime_error():
+    H, D = 2, 128
+    p = dev(synth.gen_params(1, H, D))
+    cache = torch.zeros(1, H, 2, D // 4, 4, 4, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(1, H, 16, D, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="kv_new must be float16"):
+        gemv.encode_kv(cache, x.float(), *p, SMIN, SMAX)
+    with pytest.raises(RuntimeError, match="kv_cache must be uint8"):
+        gemv.encode_kv(cache.to(torch.int32), x, *p, SMIN, SMAX)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        gemv.encode_kv(torch.zeros(1, H, 4, D // 4, 4, 4, dtype=torch.uint8, device="cuda")[:, :, ::2], x, *p, SMIN, SMAX)
+    with pytest.raises(RuntimeError, match="capacity too small"):
+        gemv.encode_kv(cache, torch.zeros(1, H, 17, D, dtype=torch.float16, device="cuda"), *p, SMIN, SMAX)
+    q = torch.zeros(1, H, 1, D, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="no free supergroup"):
+        gemv.forward_qk(q, cache, q, *p, 16, SMIN, SMAX)
+    with pytest.raises(RuntimeError, match="non-negative"):
+        gemv.forward_qk(q, cache, q, *p, -1, SMIN, SMAX)
+    with pytest.raises(RuntimeError, match="k_zp must be float16"):
+        gemv.forward_qk(q, cache, q, p[0].float(), *p[1:], 3, SMIN, SMAX)
+    bad = torch.zeros(1, H, 2, 64 // 4, 4, 4, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="head dim"):
+        gemv.forward_qk(torch.zeros(1, H, 1, 64, dtype=torch.float16, device="cuda"), bad,
+                        torch.zeros(1, H, 1, 64, dtype=torch.float16, device="cuda"),
+                        *[t[:, :64].contiguous() for t in p], 3, SMIN, SMAX)
+    assert gemv.forward_qk(q, cache, q, *p, 15, SMIN, SMAX).shape == (1, H, 16)     # last legal slot

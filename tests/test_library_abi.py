@@ -1,0 +1,66 @@
+"""CPU-side checks of the drop-in boundary: the C-ABI library loads and exports every declared symbol;
+the Python mirror refuses CPU tensors instead of falling back."""
+import os
+import re
+
+import pytest
+import torch
+
+from adkv_b200 import _lib, gemv, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "adkv_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(adkv_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 8
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/adkv_b200.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes signatures out of step with the header"
+    assert lib.adkv_abi_version() == 1
+
+
+def test_strerror_texts():
+    assert _lib.strerror(0) == "success"
+    for code in range(-7, 0):
+        assert _lib.strerror(code).startswith("adkv:")
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib._build, "LIB", "/nonexistent/libadkv_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
+
+
+def test_cpu_tensors_are_refused():
+    p = synth.gen_params(0, 2, 128)
+    cache = torch.zeros(1, 2, 2, 32, 4, 4, dtype=torch.uint8)
+    x = torch.zeros(1, 2, 8, 128, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        gemv.encode_kv(cache, x, *p, synth.SCALE_MIN, synth.SCALE_MAX)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        gemv.forward_qk(x[:, :, :1], cache, x[:, :, :1], *p, 3, synth.SCALE_MIN, synth.SCALE_MAX)
+
+
+def test_null_and_shape_errors_from_the_c_abi():
+    lib = _lib.load()
+    P = _lib.Params(1, 1, 1, 1, 1)
+    import ctypes
+    pp = ctypes.addressof(P)
+    assert lib.adkv_encode(None, 16, pp, None, 1, 1, 8, 128, 1, 4, 0, 0.1, 1.0, None) == -1
+    assert lib.adkv_encode(16, 16, pp, None, 1, 1, 8, 64, 1, 4, 0, 0.1, 1.0, None) == -2
+    assert lib.adkv_encode(16, 16, pp, None, 1, 1, 8, 128, 1, 3, 0, 0.1, 1.0, None) == -3
+    assert lib.adkv_encode(16, 16, pp, None, 1, 1, 9, 128, 1, 4, 0, 0.1, 1.0, None) == -5
+    assert lib.adkv_encode(16, 16, pp, None, 1, 1, 4, 128, 1, 4, 4, 0.1, 1.0, None) == -7
+    assert lib.adkv_forward_qk(16, 16, 16, pp, 16, 1, 3, 2, 4, 128, 1, 4, 0.1, 1.0, 0, None) == -4
+    assert lib.adkv_forward_qk(16, 24, 16, pp, 16, 1, 2, 2, 4, 128, 1, 4, 0.1, 1.0, 0, None) == -6
+    assert lib.adkv_decode_attn(16, 16, 16, 16, 16, pp, pp, None, 0, 16, 1, 2, 2, 8, 128, 1, 4,
+                                0.1, 0.1, 1.0, 0, None) == -5
