@@ -82,7 +82,7 @@ struct StreamRing {
 // ---------------------------------------------------------------------------------- K side
 
 // Replay 8 tokens (fields J0..J0+7 of the 4 words in `w`) and accumulate the partial dot products.
-template <int BITS, int G, bool EXACT, int J0, bool PARTIAL>
+template <int BITS, int G, bool EXACT, int J0, bool PARTIAL, bool GUARDED>
 __device__ __forceinline__ void k_chunk(const uint4 &w, Chan (&ch)[4], const float (&qv)[G][4],
                                         float (&part)[G][8], int count, float smin, float smax)
 {
@@ -98,7 +98,7 @@ __device__ __forceinline__ void k_chunk(const uint4 &w, Chan (&ch)[4], const flo
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float q = code_f<BITS, J0 + j>(ww[c], hi[c]);
-                const float xh = replay_step<EXACT>(q, ch[c], smin, smax);
+                const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
 #pragma unroll
                 for (int g = 0; g < G; ++g) part[g][j] = fmaf(qv[g][c], xh, part[g][j]);
             }
@@ -150,7 +150,8 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
     Chan ch[4];
-    load_chan4<EXACT>(ch, a.p, h, 4 * lane);
+    SafeRange safe;
+    load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
     float qv[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane);
@@ -168,27 +169,37 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
         const int ntok = min(kTileTok, a.T - i * kTileTok);
         float part[G][8], sum[G];
         if (ntok == kTileTok) {
-#pragma unroll
+            // not unrolled over the words of the tile: the loop body must stay resident in the
+            // instruction cache while K and V warps of many streams interleave
+            uint4 w = tile[0];
+#pragma unroll 1
             for (int wd = 0; wd < Tile<BITS>::WORDS; ++wd) {
-                const uint4 w = tile[wd * (kD / 4)];
+                const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
 #pragma unroll
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
-                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false>(w, ch, qv, part, 8, a.smin, a.smax);
-                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, false>(w, ch, qv, part, 8, a.smin, a.smax);
+                    if (safe.holds(ch)) {
+                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, false>(w, ch, qv, part, 8, a.smin, a.smax);
+                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, ch, qv, part, 8, a.smin, a.smax);
+                    } else {
+                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, true>(w, ch, qv, part, 8, a.smin, a.smax);
+                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, ch, qv, part, 8, a.smin, a.smax);
+                    }
                     reduce8<G>(part, red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
                 }
+                w = w_next;
             }
         } else {
+#pragma unroll 1
             for (int wd = 0; wd * C::TPW < ntok; ++wd) {
                 const uint4 w = tile[wd * (kD / 4)];
                 const int count = ntok - wd * C::TPW;   // valid fields in this word (may exceed TPW)
 #pragma unroll
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     if (c8 * 8 >= count) break;
-                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, true>(w, ch, qv, part, count, a.smin, a.smax);
-                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, true>(w, ch, qv, part, count, a.smin, a.smax);
+                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, true, true>(w, ch, qv, part, count, a.smin, a.smax);
+                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, ch, qv, part, count, a.smin, a.smax);
                     reduce8<G>(part, red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
@@ -233,7 +244,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
 
 // ---------------------------------------------------------------------------------- V side
 
-template <int BITS, int G, bool EXACT, int J0, bool PARTIAL>
+template <int BITS, int G, bool EXACT, int J0, bool PARTIAL, bool GUARDED>
 __device__ __forceinline__ void v_chunk(const uint4 &w, Chan (&ch)[4], const float *wts /* [G][32] smem */,
                                         int tok0, float (&acc)[G][4], int count, float smin, float smax)
 {
@@ -255,7 +266,7 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, Chan (&ch)[4], const flo
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float q = code_f<BITS, J0 + j>(ww[c], hi[c]);
-                const float xh = replay_step<EXACT>(q, ch[c], smin, smax);
+                const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
 #pragma unroll
                 for (int g = 0; g < G; ++g) acc[g][c] = fmaf(wt[g][j], xh, acc[g][c]);
             }
@@ -285,7 +296,8 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
     Chan ch[4];
-    load_chan4<EXACT>(ch, a.p, h, 4 * lane);
+    SafeRange safe;
+    load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -304,21 +316,32 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
         if (!(ok = ring.wait(i))) break;
         const uint4 *tile = ring.tile(i, lane);
         if (ntok == kTileTok) {
-#pragma unroll
+            uint4 w = tile[0];
+#pragma unroll 1
             for (int wd = 0; wd < Tile<BITS>::WORDS; ++wd) {
-                const uint4 w = tile[wd * (kD / 4)];
-                v_chunk<BITS, G, EXACT, 0, false>(w, ch, wts, wd * C::TPW, acc, 8, a.smin, a.smax);
-                if (C::TPW == 16)
-                    v_chunk<BITS, G, EXACT, 8 % C::TPW, false>(w, ch, wts, wd * C::TPW + 8, acc, 8, a.smin, a.smax);
+                const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
+#pragma unroll
+                for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
+                    const int tok0 = wd * C::TPW + c8 * 8;
+                    if (safe.holds(ch)) {
+                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, false>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                    } else {
+                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, true>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                    }
+                }
+                w = w_next;
             }
         } else {
+#pragma unroll 1
             for (int wd = 0; wd * C::TPW < ntok; ++wd) {
                 const uint4 w = tile[wd * (kD / 4)];
                 const int count = ntok - wd * C::TPW;
-                v_chunk<BITS, G, EXACT, 0, true>(w, ch, wts, wd * C::TPW, acc, count, a.smin, a.smax);
+                v_chunk<BITS, G, EXACT, 0, true, true>(w, ch, wts, wd * C::TPW, acc, count, a.smin, a.smax);
                 if (C::TPW == 16 && count > 8)
-                    v_chunk<BITS, G, EXACT, 8 % C::TPW, true>(w, ch, wts, wd * C::TPW + 8, acc, count, a.smin,
-                                                              a.smax);
+                    v_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, ch, wts, wd * C::TPW + 8, acc, count, a.smin,
+                                                                    a.smax);
             }
         }
         ring.release_and_refill(i, lane);   // also orders this tile's reads of wts before the next fill

@@ -79,23 +79,60 @@ struct Chan {
 };
 
 // Decoder side of one token: dequantise code q with the current state, then advance.
-template <bool EXACT>
+// GUARDED = false drops the eps guard and the scale clamp; the caller uses it only where
+// `SafeRange` proves both to be the identity for the tokens processed, so results are unchanged.
+template <bool EXACT, bool GUARDED>
 __device__ __forceinline__ float replay_step(float q, Chan &c, float smin, float smax)
 {
-    const float ss = fmaxf(c.s, kEps);
+    const float ss = GUARDED ? fmaxf(c.s, kEps) : c.s;
     const float rh = __fmul_rn(q, ss);
     const float xh = __fadd_rn(rh, c.zp);
+    float s_new;
     if (EXACT) {
         c.zp = __fadd_rn(c.zp, __fmul_rn(c.alpha, rh));
         const float err = __fsub_rn(fabsf(q), c.tc);
-        c.s = fminf(fmaxf(__fadd_rn(c.s, __fmul_rn(__fmul_rn(c.s, c.beta), err)), smin), smax);
+        s_new = __fadd_rn(c.s, __fmul_rn(__fmul_rn(c.s, c.beta), err));
     } else {
         c.zp = fmaf(c.alpha, rh, c.zp);
-        const float g = fmaf(c.beta, fabsf(q), c.tc);
-        c.s = fminf(fmaxf(c.s * g, smin), smax);
+        s_new = c.s * fmaf(c.beta, fabsf(q), c.tc);
     }
+    c.s = GUARDED ? fminf(fmaxf(s_new, smin), smax) : s_new;
     return xh;
 }
+
+// Interval of scales from which 8 further updates cannot leave [max(smin, eps), smax]: inside it the
+// clamp and the eps guard are the identity and the unguarded step gives bit-identical results.
+// One conservative interval per lane (intersection over its 4 channels).
+struct SafeRange {
+    float lo, hi;
+    template <int BITS>
+    __device__ __forceinline__ void init(const float (&beta)[4], const float (&target)[4], float smin, float smax)
+    {
+        lo = 0.f;
+        hi = INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float g0 = 1.f - beta[c] * target[c];                      // |q| = 0
+            const float g1 = g0 + beta[c] * float(Codec<BITS>::BIAS);        // |q| = largest code magnitude
+            const float gmn = fminf(fminf(g0, g1), 1.f), gmx = fmaxf(fmaxf(g0, g1), 1.f);
+            float pmn = gmn * gmn, pmx = gmx * gmx;                          // 8th powers
+            pmn *= pmn; pmn *= pmn;
+            pmx *= pmx; pmx *= pmx;
+            const float l = gmn > 0.f ? fmaxf(smin, kEps) / (pmn * (1.f - 2e-5f)) : INFINITY;
+            const float h = smax / (pmx * (1.f + 2e-5f));
+            lo = fmaxf(lo, l);
+            hi = fminf(hi, h);
+        }
+        if (!(lo <= hi)) { lo = INFINITY; hi = 0.f; }
+    }
+    // warp-uniform: every channel of every lane is inside its interval
+    __device__ __forceinline__ bool holds(const Chan (&ch)[4]) const
+    {
+        const float mn = fminf(fminf(ch[0].s, ch[1].s), fminf(ch[2].s, ch[3].s));
+        const float mx = fmaxf(fmaxf(ch[0].s, ch[1].s), fmaxf(ch[2].s, ch[3].s));
+        return __all_sync(kFull, mn >= lo && mx <= hi);
+    }
+};
 
 // Encoder side of one token, canonical order only (train_model.py:72, :8-17).  Returns the
 // code as a float; rh = q * max(s, eps).
@@ -211,8 +248,9 @@ struct ParamPtrs {
     const __half *zp_init, *scale_init, *alpha, *beta, *target;
 };
 
-template <bool EXACT>
-__device__ __forceinline__ void load_chan4(Chan (&ch)[4], const ParamPtrs &p, int h, int c0)
+template <int BITS, bool EXACT>
+__device__ __forceinline__ void load_chan4(Chan (&ch)[4], SafeRange &safe, const ParamPtrs &p, int h, int c0,
+                                           float smin, float smax)
 {
     const size_t off = size_t(h) * kD + c0;
     const uint2 a = *reinterpret_cast<const uint2 *>(p.zp_init + off);
@@ -223,13 +261,17 @@ __device__ __forceinline__ void load_chan4(Chan (&ch)[4], const ParamPtrs &p, in
     const __half2 *pa = reinterpret_cast<const __half2 *>(&a), *pb = reinterpret_cast<const __half2 *>(&b),
                   *pc = reinterpret_cast<const __half2 *>(&c), *pd = reinterpret_cast<const __half2 *>(&d),
                   *pe = reinterpret_cast<const __half2 *>(&e);
+    float beta[4], target[4];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const float2 za = __half22float2(pa[i]), sb = __half22float2(pb[i]), al = __half22float2(pc[i]),
                      be = __half22float2(pd[i]), tg = __half22float2(pe[i]);
         ch[2 * i] = Chan{za.x, sb.x, al.x, be.x, EXACT ? tg.x : fmaf(-be.x, tg.x, 1.0f)};
         ch[2 * i + 1] = Chan{za.y, sb.y, al.y, be.y, EXACT ? tg.y : fmaf(-be.y, tg.y, 1.0f)};
+        beta[2 * i] = be.x; beta[2 * i + 1] = be.y;
+        target[2 * i] = tg.x; target[2 * i + 1] = tg.y;
     }
+    safe.init<BITS>(beta, target, smin, smax);
 }
 
 __device__ __forceinline__ void load_half4(float (&v)[4], const __half *p)

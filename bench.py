@@ -1,0 +1,440 @@
+"""Benchmark of the ADKV decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one fused decode-attention pass (q.K^T, softmax, P.V and both appends, one launch) over one
+batch of synthetic post-RoPE-outlier K/V held as packed ADKV codes.  The default workload is the
+Llama-2-7B shape of the headline metric: 32 heads, head_dim 128, batch 128 per GPU, 4096 cached
+tokens, 4-bit codes.  With N > 1 (one process per GPU, launched by torch.distributed.run) every rank
+runs the same per-GPU batch on its own shard of sequences (no data-path collective; weak scaling,
+``--scaling strong`` splits a fixed batch instead).  Rank 0 prints one JSON line.
+
+``value``  : packed-KV bytes processed per second by the whole job, inputs resident in HBM.
+``e2e``    : the same through the public Python API with the step's q / k_new / v_new coming from
+             pinned host memory and the output copied back, copies inside the timed region.
+``roofline``: algorithmic bytes per launch / average launch time (CUDA events) against the measured
+             HBM copy bandwidth of MEASURED_PEAKS.json.
+``cpu_baseline``: the C restatement of the reference algorithm (oracle/) on the host cores, on a
+             bounded sample of the same workload; also used to check the GPU result of the sample.
+``--impl reference`` times that CPU implementation alone (the reference's CUDA file needs its own
+torch extension build and computes in fp16, and its torch path cannot travel to the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: per-GPU batch, q heads, kv heads, head dim, cached tokens, bits
+    "config2_llama2_7b_b128_t4096_4bit": dict(B=128, Hq=32, Hkv=32, D=128, T=4096, bits=4),
+    "config5_llama3_8b_gqa_b32_t32768_2bit": dict(B=32, Hq=32, Hkv=8, D=128, T=32768, bits=2),
+    "small_b8_t1024_4bit": dict(B=8, Hq=32, Hkv=32, D=128, T=1024, bits=4),
+    # profiling-sized cases: same kernels and per-stream work, a few hundred MB on the device
+    "profile_b16_t4096_4bit": dict(B=16, Hq=32, Hkv=32, D=128, T=4096, bits=4),
+    "profile_gqa_b8_t16384_2bit": dict(B=8, Hq=32, Hkv=8, D=128, T=16384, bits=2),
+}
+DEFAULT_WORKLOAD = "config2_llama2_7b_b128_t4096_4bit"
+METRIC = "fused_adkv_decode_attn_packed_kv_bandwidth"
+UNIT = "GB/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
+# summarised under profiles/ (bytes); None where no capture exists for the workload.
+NCU_TRAFFIC_BYTES = {}
+
+
+def algorithmic_bytes(w) -> int:
+    """Bytes one decode step must move: packed K and V, q and out, k_new and v_new, parameters."""
+    B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
+    return 2 * B * Hkv * T * D * bits // 8 + 2 * B * Hq * D * 2 + 2 * B * Hkv * D * 2 + 10 * Hkv * D * 2
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# --------------------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only) in a thread."""
+
+    def __init__(self, index: int, pci_bus_id: str | None = None, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.mark = [], None
+        self._stop = threading.Event()
+        self._thr = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByPciBusId(pci_bus_id.encode()) if pci_bus_id else \
+                    pynvml.nvmlDeviceGetHandleByIndex(index)
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _reasons(self, mask: int):
+        nv = self.nv
+        names = {"hw_slowdown": "nvmlClocksThrottleReasonHwSlowdown",
+                 "hw_thermal_slowdown": "nvmlClocksThrottleReasonHwThermalSlowdown",
+                 "sw_thermal_slowdown": "nvmlClocksThrottleReasonSwThermalSlowdown",
+                 "sw_power_cap": "nvmlClocksThrottleReasonSwPowerCap"}
+        return [k for k, v in names.items() if mask & getattr(nv, v, 0)]
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, mask))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self, t0: float, t1: float):
+        if self.nv is None:
+            return self._smi_fallback()
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz,
+                "reasons": self._reasons(mask), "samples": len(inside)}
+
+    def _smi_fallback(self):
+        try:
+            out = subprocess.run(["nvidia-smi", "-i", str(self.index),
+                                  "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits"],
+                                 capture_output=True, text=True, timeout=10).stdout.strip().split(",")
+            return {"sm_mhz": float(out[0]), "sm_max_mhz": float(out[1]), "reasons": [], "samples": 1,
+                    "note": "NVML unavailable: single nvidia-smi sample after the timed region"}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+
+
+# --------------------------------------------------------------------------------------- CPU arm
+
+def cpu_sample(w, n_streams: int, seed: int = 1234):
+    """Inputs of `n_streams` (batch, kv head) streams of the workload, prefilled by the C restatement."""
+    import numpy as np
+
+    from adkv_b200 import synth
+    from oracle import adkv_oracle as orc
+    from oracle import c_oracle
+    Hkv, G, D, T, bits = w["Hkv"], w["Hq"] // w["Hkv"], w["D"], w["T"], w["bits"]
+    # the sample is laid out as a batch of n_streams sequences with one kv head each
+    k = synth.gen_kv(seed, n_streams, 1, T + 1, D).numpy()
+    v = synth.gen_kv(seed + 1, n_streams, 1, T + 1, D).numpy()
+    q = synth.gen_q(seed + 2, n_streams, G, D).numpy()[:, :, 0]
+    kp = tuple(t.float().numpy() for t in synth.gen_params(seed + 3, 1, D, bits))
+    vp = tuple(t.float().numpy() for t in synth.gen_params(seed + 4, 1, D, bits))
+    ns = orc.n_super_for(T + 1, bits)
+    kc = np.zeros(orc.cache_shape(n_streams, 1, ns, D), np.uint8)
+    vc = np.zeros_like(kc)
+    c_oracle.encode(kc, k[:, :, :T], kp, bits, synth.SCALE_MIN, synth.SCALE_MAX)
+    c_oracle.encode(vc, v[:, :, :T], vp, bits, synth.SCALE_MIN, synth.SCALE_MAX)
+    return dict(k=k, v=v, q=q, kp=kp, vp=vp, kc=kc, vc=vc, n=n_streams)
+
+
+def cpu_step(w, s):
+    from adkv_b200 import synth
+    from oracle import c_oracle
+    T = w["T"]
+    return c_oracle.decode_attn(s["q"], s["kc"], s["vc"], s["k"][:, :, T], s["v"][:, :, T], s["kp"], s["vp"], T,
+                                w["D"] ** -0.5, w["bits"], synth.SCALE_MIN, synth.SCALE_MAX)
+
+
+def sample_bytes(w, n_streams: int) -> int:
+    ws = dict(w, B=n_streams, Hkv=1, Hq=w["Hq"] // w["Hkv"])
+    return algorithmic_bytes(ws)
+
+
+def pick_sample_streams(w, target_s: float) -> int:
+    """Streams whose decode takes about `target_s` seconds of host time, from a 1-stream-per-thread probe."""
+    from oracle import c_oracle
+    c_oracle.build()
+    thr = c_oracle.num_threads()
+    probe = cpu_sample(w, thr)
+    cpu_step(w, probe)
+    t0 = time.perf_counter()
+    cpu_step(w, probe)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    n = int(target_s / dt) * thr
+    return max(thr, min(n, w["B"] * w["Hkv"]))
+
+
+def run_reference(args, w, name):
+    """The reference algorithm on the host cores (C restatement, all threads), bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import c_oracle
+    # size the per-step sample so that warm-up + timed steps take about a minute of host time
+    n = pick_sample_streams(w, target_s=min(2.0, max(0.05, 60.0 / (args.steps + args.warmup))))
+    s = cpu_sample(w, n)
+    for _ in range(args.warmup):
+        cpu_step(w, s)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(w, s)
+    dt = time.perf_counter() - t0
+    val = sample_bytes(w, n) * args.steps / dt / 1e9
+    sample = f"{n} of {w['B'] * w['Hkv']} (batch, kv-head) streams of the workload per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": dict(workload=name, **w),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": c_oracle.num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+# --------------------------------------------------------------------------------------- GPU arm
+
+def build_gpu_state(w, seed, device, torch):
+    """Caches prefilled by the encode kernel from on-device synthetic K/V, plus the step's inputs."""
+    from adkv_b200 import gemv, synth
+    B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
+    ns = gemv.n_super_for(T + 1, bits)
+    kp = synth.gen_params(seed + 3, Hkv, D, bits, device=device)
+    vp = synth.gen_params(seed + 4, Hkv, D, bits, device=device)
+    kc = torch.zeros((B, Hkv, ns, D // 4, 4, 4), dtype=torch.uint8, device=device)
+    vc = torch.zeros_like(kc)
+    chunk = max(1, min(B, (1 << 28) // (Hkv * T * D)))      # keep generator temporaries around 1 GiB
+    for b0 in range(0, B, chunk):
+        b1 = min(B, b0 + chunk)
+        k = synth.gen_kv(seed + 10 * b0, b1 - b0, Hkv, T, D, device=device)
+        gemv.encode_kv(kc[b0:b1], k, *kp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+        v = synth.gen_kv(seed + 10 * b0 + 1, b1 - b0, Hkv, T, D, device=device)
+        gemv.encode_kv(vc[b0:b1], v, *vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+        del k, v
+    q = synth.gen_q(seed + 2, B, Hq, D, device=device)
+    kn = synth.gen_kv(seed + 5, B, Hkv, 1, D, device=device, pos0=T)
+    vn = synth.gen_kv(seed + 6, B, Hkv, 1, D, device=device, pos0=T)
+    torch.cuda.synchronize(device)
+    return dict(kc=kc, vc=vc, kp=kp, vp=vp, q=q, kn=kn, vn=vn)
+
+
+def check_against_oracle(w, st, out, n_streams, torch):
+    """Compare the GPU output and appended codes of the first streams with the C restatement; time it."""
+    import numpy as np
+
+    from adkv_b200 import synth
+    from oracle import c_oracle
+    Hq, Hkv, D, T, bits = w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
+    G = Hq // Hkv
+    nb = max(1, min(w["B"], (n_streams + Hkv - 1) // Hkv))
+    n_streams = nb * Hkv
+    kc_after = st["kc"][:nb].cpu().numpy()
+    vc_after = st["vc"][:nb].cpu().numpy()
+    kc, vc = kc_after.copy(), vc_after.copy()       # slot T already holds the GPU's append; the CPU rewrites it
+    f = lambda ps: tuple(p.float().cpu().numpy() for p in ps)
+    args = (st["q"][:nb, :, 0].cpu().numpy(), kc, vc, st["kn"][:nb, :, 0].cpu().numpy(),
+            st["vn"][:nb, :, 0].cpu().numpy(), f(st["kp"]), f(st["vp"]), T, D ** -0.5, bits,
+            synth.SCALE_MIN, synth.SCALE_MAX)
+    c_oracle.decode_attn(*args)                     # warm the threads and page in the sample
+    t0 = time.perf_counter()
+    want = c_oracle.decode_attn(*args)
+    dt = time.perf_counter() - t0
+    got = out[:nb].float().cpu().numpy()
+    tol = 2e-3 * max(1.0, float(np.abs(want).max()))
+    ok = bool(np.allclose(got, want, rtol=2e-3, atol=tol)) and np.array_equal(kc, kc_after) and \
+        np.array_equal(vc, vc_after)
+    return ok, dt, n_streams, c_oracle.num_threads()
+
+
+def run_ours(args, w, name):
+    import torch
+    import torch.distributed as dist
+
+    from adkv_b200 import gemv, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    w = dict(w)
+    if args.scaling == "strong" and world > 1:
+        assert w["B"] % world == 0, "strong scaling splits the batch evenly"
+        w["B"] //= world
+    st = build_gpu_state(w, seed=1000 + 7919 * rank, device=device, torch=torch)
+    B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
+    scaling = D ** -0.5
+    fast = args.replay == "fast"
+    out = torch.empty((B, Hq, D), dtype=torch.float16, device=device)
+
+    def step():
+        gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T, scaling,
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- device-resident timing
+    prop = torch.cuda.get_device_properties(device)
+    try:
+        bus_id = f"{prop.pci_domain_id:08x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+    except AttributeError:
+        bus_id = None
+    sampler = ClockSampler(local, bus_id)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    t_wall0 = time.perf_counter()
+    ev[0].record()
+    for i in range(args.steps):
+        step()
+        ev[i + 1].record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    sampler.stop()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    assert gemv.device_status(device) == 0, "a kernel gave up on a bounded wait"
+
+    # ---- end to end through the public API: host inputs in, host output back, every step
+    hq, hk, hv = (t.cpu().pin_memory() for t in (st["q"], st["kn"], st["vn"]))
+    hout = torch.empty((B, Hq, D), dtype=torch.float16).pin_memory()
+    dq, dk_, dv_ = (torch.empty_like(t) for t in (st["q"], st["kn"], st["vn"]))
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk_.copy_(hk, non_blocking=True)
+        dv_.copy_(hv, non_blocking=True)
+        gemv.decode_attn(dq, st["kc"], st["vc"], dk_, dv_, st["kp"], st["vp"], T, scaling,
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out)
+        hout.copy_(out, non_blocking=True)
+
+    for _ in range(max(3, min(args.warmup, 5))):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = t.tolist()
+
+    bytes_rank = algorithmic_bytes(w)
+    res = None
+    if rank == 0:
+        value = bytes_rank * world * args.steps / (total_ms * 1e-3) / 1e9
+        e2e_val = bytes_rank * world * args.steps / (e2e_ms * 1e-3) / 1e9
+        peak, peak_src = measured_peak_gbs()
+        avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
+        achieved = bytes_rank / (avg_launch_ms * 1e-3) / 1e9
+        res = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload=name, per_gpu=w, global_batch=w["B"] * world, replay=args.replay,
+                           sharding="batch, one process per GPU, no collective on the data path",
+                           l2="inputs (packed K+V per step) larger than L2; no flush needed"
+                           if bytes_rank > 200e6 else "inputs smaller than L2: cache-resident timing"),
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": world * (hq.numel() + hk.numel() + hv.numel()) * 2,
+                    "d2h_bytes_per_step": world * hout.numel() * 2, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": args.steps,
+            "decode_tokens_per_s": {"one_layer": w["B"] * world * args.steps / (total_ms * 1e-3),
+                                    "over_32_layers": w["B"] * world * args.steps / (total_ms * 1e-3) / 32},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "frac_of_8TBps_nominal": achieved / 8000.0,
+                         "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel": "decode_attn_kernel",
+                         "algorithmic_bytes_per_launch": bytes_rank, "avg_launch_ms": avg_launch_ms,
+                         "median_launch_ms": statistics.median(per_launch_ms)},
+            "clocks": sampler.summary(t_wall0, t_wall1),
+        }
+        if world == 1 and not args.no_cpu:
+            n = pick_sample_streams(w, target_s=args.cpu_seconds)
+            ok, dt, n_used, cores = check_against_oracle(w, st, out, n, torch)
+            res["cpu_baseline"] = {"value": sample_bytes(w, n_used) / dt / 1e9, "unit": UNIT, "cores": cores,
+                                   "kind": "port", "seconds": dt,
+                                   "sample": f"{n_used} of {B * Hkv} (batch, kv-head) streams of the workload, "
+                                             "one decode step, C restatement with OpenMP"}
+            res["parity_check"] = "ok" if ok else "FAILED"
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if res is not None and res.get("parity_check") == "FAILED":
+        sys.exit(1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--replay", choices=["exact", "fast"], default="exact")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        # not launched by torch.distributed.run: do it ourselves, one process per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 1000),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+    if args.impl == "reference":
+        run_reference(args, w, args.workload)
+    else:
+        run_ours(args, w, args.workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -166,6 +166,34 @@ def test_decode_attn(B, Hq, Hkv, T, bits, with_mask, fast):
         assert np.array_equal(dk.cpu().numpy(), wk) and np.array_equal(dv.cpu().numpy(), wv)
 
 
+@pytest.mark.parametrize("bits", [4, 2])
+def test_decode_with_scales_at_both_clamps(bits):
+    """Channels whose scale sits at scale_min (all-zero input) or scale_max (saturating input) during the
+    replay: the kernels' unguarded fast body must hand over to the guarded one without changing a bit."""
+    B, H, T, D = 2, 2, 333, 128
+    case = make_case(77, B, H, H, T, bits)
+    for name in ("k", "v"):
+        x = case[name].float()
+        x[..., :16] = 0.0                       # q = 0 forever: scale decays to scale_min
+        x[..., 16:32] *= 400.0                  # saturated codes: scale grows to scale_max
+        x[..., 200:, 32:48] = 0.0               # decays only in the second part of the sequence
+        case[name] = x.half()
+    kc, vc = oracle_prefill(case)
+    scaling = 0.05
+    wk, wv = kc.copy(), vc.copy()
+    want = orc.decode_attn(case["q"][:, :, 0].numpy(), wk, wv, case["k"][:, :, T].numpy(), case["v"][:, :, T].numpy(),
+                           np_params(case["kp"]), np_params(case["vp"]), T, scaling, bits=bits,
+                           scale_min=SMIN, scale_max=SMAX)
+    _, st = orc.replay(vc, T, np_params(case["vp"]), bits, SMIN, SMAX)
+    assert np.isclose(st.s.min(), SMIN) and np.isclose(st.s.max(), SMAX)      # both clamps really are active
+    dk, dv = dev(kc), dev(vc)
+    got = gemv.decode_attn(dev(case["q"]), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
+                           dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits)
+    _status_ok()
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    assert np.array_equal(dk.cpu().numpy(), wk) and np.array_equal(dv.cpu().numpy(), wv)
+
+
 def test_decode_steps_chain_like_generation():
     """Prefill with the kernel, then 40 fused decode steps; caches stay bit-identical to the oracle's."""
     B, H, T0, steps, bits, D = 2, 2, 21, 40, 4, 128
