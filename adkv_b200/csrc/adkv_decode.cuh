@@ -83,13 +83,17 @@ struct StreamRing {
 
 // Replay 8 tokens (fields J0..J0+7 of the 4 words in `w`) and accumulate the partial dot products.
 template <int BITS, int G, bool EXACT, int J0, bool PARTIAL, bool GUARDED>
-__device__ __forceinline__ void k_chunk(const uint4 &w, Chan (&ch)[4], const float (&qv)[G][4],
-                                        float (&part)[G][8], int count, float smin, float smax)
+__device__ __forceinline__ void k_chunk(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
+                                        const float (&qv)[G][4], float (&part)[G][8], int count, float smin,
+                                        float smax)
 {
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    uint32_t hi[4];
+    uint32_t lo[4], hi[4];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) hi[c] = ww[c] >> Codec<BITS>::HI_SHIFT;
+    for (int c = 0; c < 4; ++c) {
+        lo[c] = field_group<BITS, J0>(ww[c]);
+        hi[c] = field_group<BITS, J0 + 4>(ww[c]);
+    }
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
 #pragma unroll
@@ -97,7 +101,7 @@ __device__ __forceinline__ void k_chunk(const uint4 &w, Chan (&ch)[4], const flo
         if (!PARTIAL || J0 + j < count) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float q = code_f<BITS, J0 + j>(ww[c], hi[c]);
+                const float q = fc.template code<j % 4>(j < 4 ? lo[c] : hi[c]);
                 const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
 #pragma unroll
                 for (int g = 0; g < G; ++g) part[g][j] = fmaf(qv[g][c], xh, part[g][j]);
@@ -151,6 +155,8 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
     const int bh = b * a.Hkv + h;
     Chan ch[4];
     SafeRange safe;
+    FieldConsts<BITS> fc;
+    fc.init();
     load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
     float qv[G][4];
 #pragma unroll
@@ -178,11 +184,11 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
 #pragma unroll
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     if (safe.holds(ch)) {
-                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, false>(w, ch, qv, part, 8, a.smin, a.smax);
-                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, ch, qv, part, 8, a.smin, a.smax);
+                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, false>(w, fc, ch, qv, part, 8, a.smin, a.smax);
+                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, fc, ch, qv, part, 8, a.smin, a.smax);
                     } else {
-                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, true>(w, ch, qv, part, 8, a.smin, a.smax);
-                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, ch, qv, part, 8, a.smin, a.smax);
+                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, true>(w, fc, ch, qv, part, 8, a.smin, a.smax);
+                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, fc, ch, qv, part, 8, a.smin, a.smax);
                     }
                     reduce8<G>(part, red, lane, sum);
 #pragma unroll
@@ -198,8 +204,8 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
 #pragma unroll
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     if (c8 * 8 >= count) break;
-                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, true, true>(w, ch, qv, part, count, a.smin, a.smax);
-                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, ch, qv, part, count, a.smin, a.smax);
+                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, true, true>(w, fc, ch, qv, part, count, a.smin, a.smax);
+                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, fc, ch, qv, part, count, a.smin, a.smax);
                     reduce8<G>(part, red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
@@ -245,27 +251,31 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
 // ---------------------------------------------------------------------------------- V side
 
 template <int BITS, int G, bool EXACT, int J0, bool PARTIAL, bool GUARDED>
-__device__ __forceinline__ void v_chunk(const uint4 &w, Chan (&ch)[4], const float *wts /* [G][32] smem */,
-                                        int tok0, float (&acc)[G][4], int count, float smin, float smax)
+__device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
+                                        const float *wts /* [G][32] smem */, int tok0, float (&acc)[G][4],
+                                        int count, float smin, float smax)
 {
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    uint32_t hi[4];
+    uint32_t lo[4], hi[4];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) hi[c] = ww[c] >> Codec<BITS>::HI_SHIFT;
+    for (int c = 0; c < 4; ++c) {
+        lo[c] = field_group<BITS, J0>(ww[c]);
+        hi[c] = field_group<BITS, J0 + 4>(ww[c]);
+    }
     float wt[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const float4 lo = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0);
-        const float4 up = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0 + 4);
-        wt[g][0] = lo.x; wt[g][1] = lo.y; wt[g][2] = lo.z; wt[g][3] = lo.w;
-        wt[g][4] = up.x; wt[g][5] = up.y; wt[g][6] = up.z; wt[g][7] = up.w;
+        const float4 a = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0);
+        const float4 b = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0 + 4);
+        wt[g][0] = a.x; wt[g][1] = a.y; wt[g][2] = a.z; wt[g][3] = a.w;
+        wt[g][4] = b.x; wt[g][5] = b.y; wt[g][6] = b.z; wt[g][7] = b.w;
     }
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
         if (!PARTIAL || J0 + j < count) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float q = code_f<BITS, J0 + j>(ww[c], hi[c]);
+                const float q = fc.template code<j % 4>(j < 4 ? lo[c] : hi[c]);
                 const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
 #pragma unroll
                 for (int g = 0; g < G; ++g) acc[g][c] = fmaf(wt[g][j], xh, acc[g][c]);
@@ -297,6 +307,8 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
     const int bh = b * a.Hkv + h;
     Chan ch[4];
     SafeRange safe;
+    FieldConsts<BITS> fc;
+    fc.init();
     load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
     float acc[G][4];
 #pragma unroll
@@ -324,11 +336,11 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     const int tok0 = wd * C::TPW + c8 * 8;
                     if (safe.holds(ch)) {
-                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, false>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
-                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, false>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
                     } else {
-                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, true>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
-                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
                     }
                 }
                 w = w_next;
@@ -338,9 +350,9 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
             for (int wd = 0; wd * C::TPW < ntok; ++wd) {
                 const uint4 w = tile[wd * (kD / 4)];
                 const int count = ntok - wd * C::TPW;
-                v_chunk<BITS, G, EXACT, 0, true, true>(w, ch, wts, wd * C::TPW, acc, count, a.smin, a.smax);
+                v_chunk<BITS, G, EXACT, 0, true, true>(w, fc, ch, wts, wd * C::TPW, acc, count, a.smin, a.smax);
                 if (C::TPW == 16 && count > 8)
-                    v_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, ch, wts, wd * C::TPW + 8, acc, count, a.smin,
+                    v_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, fc, ch, wts, wd * C::TPW + 8, acc, count, a.smin,
                                                                     a.smax);
             }
         }

@@ -41,27 +41,48 @@ struct Codec {
     static constexpr int TPW = 32 / BITS;
     static constexpr int BIAS = 1 << (BITS - 1);
     static constexpr uint32_t FIELD = (1u << BITS) - 1u;
-    static constexpr int DIRECT = 23 / BITS;   // fields that lie inside the fp32 mantissa in place
-    static constexpr int HI_SHIFT = 12;        // the remaining fields are taken from word >> 12
     __host__ __device__ static constexpr float qlo() { return -float(BIAS); }
     __host__ __device__ static constexpr float qhi() { return float(BIAS - 1); }
 };
 
-// Code of token J (compile time) as a float, without an integer-to-float conversion: the
-// field is masked in place into the mantissa of 2^(23-p) (p = bit position of the field), which
-// makes the float 2^(23-p) + field; subtracting 2^(23-p) + BIAS is exact.
-template <int BITS, int J>
-__device__ __forceinline__ float code_f(uint32_t w, uint32_t whi)
+// A value the optimiser cannot see through: keeps a constant in a register for the whole kernel
+// instead of being re-materialised as an immediate at every use.
+__device__ __forceinline__ uint32_t opaque_u32(uint32_t v)
 {
-    using C = Codec<BITS>;
-    constexpr bool direct = J < C::DIRECT;
-    constexpr int P = BITS * (direct ? J : J - C::HI_SHIFT / BITS);
-    static_assert(P + BITS <= 23, "field must lie inside the mantissa");
-    constexpr uint32_t m = C::FIELD << P;
-    constexpr uint32_t e = uint32_t(127 + 23 - P) << 23;
-    const float f = __uint_as_float(((direct ? w : whi) & m) | e);
-    constexpr float c = float(1u << (23 - P)) + float(C::BIAS);
-    return __fsub_rn(f, c);
+    uint32_t r;
+    asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+
+// Codes as floats without integer-to-float conversions.  A group of 4 consecutive fields is taken
+// from the word shifted down to bit 0; field k of the group then sits at bit p = BITS*k inside the
+// mantissa.  Masking it in place into the bit pattern of 2^(23-p) gives the float 2^(23-p) + field,
+// and subtracting 2^(23-p) + BIAS is exact.  The exponent pattern lives in a register and the mask is
+// an immediate so that the mask-and-merge is a single three-input logic operation.
+template <int BITS>
+struct FieldConsts {
+    uint32_t e[4];
+    __device__ __forceinline__ void init()
+    {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) e[k] = opaque_u32(uint32_t(127 + 23 - BITS * k) << 23);
+    }
+    template <int K>
+    __device__ __forceinline__ float code(uint32_t group) const
+    {
+        constexpr float c = float(1u << (23 - BITS * K)) + float(Codec<BITS>::BIAS);
+        uint32_t bits;
+        // (group & mask) | exponent as ONE lop3 (the compiler otherwise emits two): LUT 0xEA = (a & b) | c
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(bits) : "r"(group), "n"(Codec<BITS>::FIELD << (BITS * K)), "r"(e[K]));
+        return __fsub_rn(__uint_as_float(bits), c);
+    }
+};
+
+// Field J (0..TPW-1) of word w: group J/4 shifted to bit 0.
+template <int BITS, int J>
+__device__ __forceinline__ uint32_t field_group(uint32_t w)
+{
+    return (J / 4 == 0) ? w : (w >> (BITS * 4 * (J / 4)));
 }
 
 template <int BITS>
