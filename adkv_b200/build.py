@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import os
 import shutil
+from concurrent.futures import ThreadPoolExecutor
 import subprocess
 import sys
 
@@ -14,11 +15,12 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libadkv_b200.so")
-SOURCES = ["adkv_kernels.cu"]
-HEADERS = ["adkv_device.cuh", "adkv_decode.cuh", os.path.join("..", "..", "include", "adkv_b200.h")]
+SOURCES = ["adkv_capi.cu", "adkv_encode.cu", "adkv_fused.cu", "adkv_unfused.cu"]
+HEADERS = ["adkv_device.cuh", "adkv_decode.cuh", "adkv_host.h", os.path.join("..", "..", "include", "adkv_b200.h")]
+OBJ_DIR = os.path.join(PKG, "build")
 
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-              "-Xcompiler", "-fPIC", "-shared"]
+              "-Xcompiler", "-fPIC"]
 
 
 def _nvcc() -> str:
@@ -40,10 +42,24 @@ def build(force: bool = False, verbose: bool = False, extra: list[str] | None = 
     if not force and not is_stale():
         return LIB
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc()] + NVCC_FLAGS + (extra or []) + [os.path.join(CSRC, f) for f in SOURCES] + ["-o", LIB]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    nvcc = _nvcc()
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        cmd = [nvcc] + NVCC_FLAGS + (extra or []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+        return obj
+
+    # the translation units are independent: compile them side by side, then link
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
+    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a"] + objs + ["-o", LIB]
     if verbose:
-        print(" ".join(cmd), flush=True)
-    subprocess.check_call(cmd)
+        print(" ".join(link), flush=True)
+    subprocess.check_call(link)
     return LIB
 
 

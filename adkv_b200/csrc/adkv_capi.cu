@@ -1,0 +1,39 @@
+// Part of libadkv_b200.so (sm_100a).  See include/adkv_b200.h for the contract of every entry point
+// and the reference interface each one replaces.
+#include "adkv_host.h"
+
+ADKV_HIDDEN int adkv_tu_status_fused(int *out);
+ADKV_HIDDEN int adkv_tu_status_unfused(int *out);
+
+extern "C" {
+
+int adkv_abi_version(void) { return ADKV_ABI_VERSION; }
+
+const char *adkv_strerror(int code)
+{
+    switch (code) {
+    case 0: return "success";
+    case ADKV_E_NULL: return "adkv: a required pointer is NULL";
+    case ADKV_E_HEAD_DIM: return "adkv: head dim not supported by this build (D must be 128)";
+    case ADKV_E_BITS: return "adkv: bits must be 2 or 4";
+    case ADKV_E_SHAPE: return "adkv: invalid sizes (negative, Hq not a multiple of Hkv, or group size not in {1,2,4,8})";
+    case ADKV_E_CAPACITY: return "adkv: cache capacity too small for the tokens to be written";
+    case ADKV_E_ALIGN: return "adkv: pointer not sufficiently aligned (cache 16 bytes, fp16 rows 8 bytes)";
+    case ADKV_E_START: return "adkv: t_start > 0 needs a tail state";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "adkv: unknown error";
+    }
+}
+
+int adkv_device_status(int *status, void *stream)
+{
+    if (!status) return ADKV_E_NULL;
+    const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return int(e);
+    int a = 0, b = 0;
+    if (int rc = adkv_tu_status_fused(&a)) return rc;
+    if (int rc = adkv_tu_status_unfused(&b)) return rc;
+    *status = a ? a : b;
+    return 0;
+}
+
+}  // extern "C"

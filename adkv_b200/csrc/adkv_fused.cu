@@ -1,0 +1,183 @@
+// Part of libadkv_b200.so (sm_100a).  See include/adkv_b200.h for the contract of every entry point
+// and the reference interface each one replaces.
+#include "adkv_host.h"
+
+#include "adkv_decode.cuh"
+
+namespace adkv {
+
+// =========================================================================================
+// Fused decode step: one CTA per (batch, kv head); warp 0 scans K, warp 1 scans V.
+
+template <int G>
+struct FusedShared {
+    float lring[kLogitSlots][G][kTileTok];
+    uint64_t lfull[kLogitSlots], lempty[kLogitSlots];
+};
+
+template <int G>
+struct RingSink {
+    FusedShared<G> *sh;
+    int slot;
+    __device__ __forceinline__ bool begin_tile(int i)
+    {
+        slot = i % kLogitSlots;
+        return mbar_wait_bounded(&sh->lempty[slot], ((i / kLogitSlots) & 1) ^ 1, kStatLEmptyWait);
+    }
+    __device__ __forceinline__ void put8(int, int g, int tok, float v, int lane)
+    {
+        if (lane < 8) sh->lring[slot][g][tok + lane] = v;
+    }
+    __device__ __forceinline__ void end_tile(int, int lane)
+    {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->lfull[slot]);
+    }
+    __device__ __forceinline__ void put_self(int g, float v) { sh->lring[slot][g][0] = v; }
+    __device__ __forceinline__ void finish(int lane) { end_tile(0, lane); }
+};
+
+template <int G>
+struct SoftmaxSrc {
+    FusedShared<G> *sh;
+    float *wts;            // [G][32]
+    const float *mask;     // row of this batch or nullptr
+    float scale2;          // scaling * log2(e)
+    int n_tiles;
+    float m[G], l[G];
+
+    __device__ __forceinline__ void init()
+    {
+#pragma unroll
+        for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+    }
+    // online-softmax update of head g with this lane's logit v (already in log2 units, -inf if invalid)
+    __device__ __forceinline__ float update(int g, float v, float (&acc)[G][4])
+    {
+        const float m_new = fmaxf(m[g], warp_max(v));
+        const bool dead = (m_new == -INFINITY);
+        const float corr = dead ? 1.f : exp2f(m[g] - m_new);
+        const float pw = dead ? 0.f : exp2f(v - m_new);
+        l[g] = fmaf(l[g], corr, warp_sum(pw));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[g][c] *= corr;
+        m[g] = m_new;
+        return pw;
+    }
+    __device__ __forceinline__ bool tile_weights(int i, int ntok, int lane, float (&acc)[G][4])
+    {
+        const int slot = i % kLogitSlots;
+        const float mk = (mask && lane < ntok) ? mask[i * kTileTok + lane] * 1.4426950408889634f : 0.f;
+        if (!mbar_wait_bounded(&sh->lfull[slot], (i / kLogitSlots) & 1, kStatLFullWait)) return false;
+        float x[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) x[g] = sh->lring[slot][g][lane];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->lempty[slot]);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float v = lane < ntok ? fmaf(x[g], scale2, mk) : -INFINITY;
+            wts[g * kTileTok + lane] = update(g, v, acc);
+        }
+        __syncwarp();
+        return true;
+    }
+    __device__ __forceinline__ bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
+    {
+        const int slot = n_tiles % kLogitSlots;
+        if (!mbar_wait_bounded(&sh->lfull[slot], (n_tiles / kLogitSlots) & 1, kStatLFullWait)) return false;
+        const float mk = mask ? mask[T] * 1.4426950408889634f : 0.f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float v = fmaf(sh->lring[slot][g][0], scale2, mk);
+            // all lanes hold the same v: update() would count it 32 times, so do it by hand
+            const float m_new = fmaxf(m[g], v);
+            const bool dead = (m_new == -INFINITY);
+            const float corr = dead ? 1.f : exp2f(m[g] - m_new);
+            const float pw = dead ? 0.f : exp2f(v - m_new);
+            l[g] = fmaf(l[g], corr, pw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[g][c] *= corr;
+            m[g] = m_new;
+            w_self[g] = pw;
+        }
+        return true;
+    }
+    __device__ __forceinline__ float norm(int g) const { return l[g]; }
+};
+
+template <int BITS, int G, bool EXACT>
+__global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
+                                                         long long mask_stride_b, float scaling)
+{
+    __shared__ alignas(128) uint8_t kbuf[kStages * Tile<BITS>::BYTES];
+    __shared__ alignas(128) uint8_t vbuf[kStages * Tile<BITS>::BYTES];
+    __shared__ alignas(16) float red[8 * 36];
+    __shared__ alignas(16) float wts[G * kTileTok];
+    __shared__ FusedShared<G> fs;
+    __shared__ uint64_t kbar[kStages], vbar[kStages];
+
+    const int bh = blockIdx.x, b = bh / ka.Hkv, h = bh % ka.Hkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) { mbar_init(&kbar[i], 1); mbar_init(&vbar[i], 1); }
+        for (int i = 0; i < kLogitSlots; ++i) { mbar_init(&fs.lfull[i], 1); mbar_init(&fs.lempty[i], 1); }
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (warp == 0) {
+        RingSink<G> sink{&fs, 0};
+        k_warp<BITS, G, EXACT>(ka, b, h, lane, kbuf, kbar, red, sink);
+    } else {
+        SoftmaxSrc<G> src;
+        src.sh = &fs;
+        src.wts = wts;
+        src.mask = mask ? mask + size_t(b) * mask_stride_b : nullptr;
+        src.scale2 = scaling * 1.4426950408889634f;
+        src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
+        src.init();
+        v_warp<BITS, G, EXACT>(va, b, h, lane, vbuf, vbar, wts, src);
+    }
+}
+
+}  // namespace adkv
+
+using namespace adkv;
+
+// Status word of this translation unit (read and cleared by adkv_device_status).
+ADKV_HIDDEN int adkv_tu_status_fused(int *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
+    if (e != cudaSuccess) return int(e);
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+extern "C" {
+
+int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                     const adkv_params *kp, const adkv_params *vp, const void *mask, long long mask_stride_b,
+                     void *out, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scaling,
+                     float scale_min, float scale_max, unsigned flags, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !params_ok(kp) || !params_ok(vp))
+        return ADKV_E_NULL;
+    if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
+        !aligned8(v_new) || !params_aligned(kp) || !params_aligned(vp))
+        return ADKV_E_ALIGN;
+    if (B == 0) return 0;
+    const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+    const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
+                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    ADKV_DISPATCH(bits, exact, Hq / Hkv,
+                  (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(
+                      ka, va, static_cast<const float *>(mask), mask_stride_b, scaling)))
+    return launch_status();
+}
+
+}  // extern "C"

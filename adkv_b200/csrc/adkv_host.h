@@ -1,0 +1,64 @@
+// Host-side helpers shared by the translation units of libadkv_b200.so.
+#pragma once
+#include "../../include/adkv_b200.h"
+#include "adkv_device.cuh"
+
+#define ADKV_HIDDEN __attribute__((visibility("hidden")))
+
+namespace adkv {
+
+static inline ParamPtrs to_ptrs(const adkv_params *p)
+{
+    return ParamPtrs{static_cast<const __half *>(p->zp_init), static_cast<const __half *>(p->scale_init),
+                     static_cast<const __half *>(p->alpha), static_cast<const __half *>(p->beta),
+                     static_cast<const __half *>(p->target)};
+}
+
+static inline bool params_ok(const adkv_params *p)
+{
+    return p && p->zp_init && p->scale_init && p->alpha && p->beta && p->target;
+}
+
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline bool aligned8(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
+
+static inline bool params_aligned(const adkv_params *p)
+{
+    return aligned8(p->zp_init) && aligned8(p->scale_init) && aligned8(p->alpha) && aligned8(p->beta) &&
+           aligned8(p->target);
+}
+
+static inline int launch_status()
+{
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+static inline int check_common(int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, int n_written_end)
+{
+    if (D != kD) return ADKV_E_HEAD_DIM;
+    if (bits != 2 && bits != 4) return ADKV_E_BITS;
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || T < 0 || n_super_cap < 0 || Hq % Hkv != 0) return ADKV_E_SHAPE;
+    const int tpw = 32 / bits;
+    if ((long long)(n_written_end + tpw - 1) / tpw > (long long)n_super_cap) return ADKV_E_CAPACITY;
+    return 0;
+}
+
+// Dispatch over (bits, group size, arithmetic).
+#define ADKV_DISPATCH_G(BITS_, EXACT_, G_, CALL) \
+    switch (G_) {                                \
+    case 1: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 1; CALL; } break; \
+    case 2: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 2; CALL; } break; \
+    case 4: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 4; CALL; } break; \
+    case 8: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 8; CALL; } break; \
+    default: return ADKV_E_SHAPE;                \
+    }
+#define ADKV_DISPATCH(bits_, exact_, G_, CALL)                            \
+    if (bits_ == 4) {                                                     \
+        if (exact_) { ADKV_DISPATCH_G(4, true, G_, CALL) } else { ADKV_DISPATCH_G(4, false, G_, CALL) } \
+    } else {                                                              \
+        if (exact_) { ADKV_DISPATCH_G(2, true, G_, CALL) } else { ADKV_DISPATCH_G(2, false, G_, CALL) } \
+    }
+
+
+}  // namespace adkv

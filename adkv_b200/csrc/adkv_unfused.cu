@@ -1,0 +1,150 @@
+// Part of libadkv_b200.so (sm_100a).  See include/adkv_b200.h for the contract of every entry point
+// and the reference interface each one replaces.
+#include "adkv_host.h"
+
+#include "adkv_decode.cuh"
+
+namespace adkv {
+
+// =========================================================================================
+// Unfused entry points (the reference's two-kernel decode): 4 streams per CTA, one warp each.
+
+constexpr int kStreamsPerCta = 4;
+
+template <int G>
+struct GlobalLogitSink {
+    __half *row[G];   // logits row of each q head of this stream: [T+1]
+    int T;
+    __device__ __forceinline__ bool begin_tile(int) { return true; }
+    __device__ __forceinline__ void put8(int i, int g, int tok, float v, int lane)
+    {
+        const int t = i * kTileTok + tok + lane;
+        if (lane < 8 && t < T) row[g][t] = __float2half_rn(v);
+    }
+    __device__ __forceinline__ void end_tile(int, int) {}
+    __device__ __forceinline__ void put_self(int g, float v) { row[g][T] = __float2half_rn(v); }
+    __device__ __forceinline__ void finish(int) {}
+};
+
+template <int BITS, int G, bool EXACT>
+__global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs ka, __half *__restrict__ logits,
+                                                                         int n_streams)
+{
+    __shared__ alignas(128) uint8_t kbuf[kStreamsPerCta][kStages * Tile<BITS>::BYTES];
+    __shared__ alignas(16) float red[kStreamsPerCta][8 * 36];
+    __shared__ uint64_t kbar[kStreamsPerCta][kStages];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+        for (int i = 0; i < kStages; ++i) mbar_init(&kbar[warp][i], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const int bh = blockIdx.x * kStreamsPerCta + warp;
+    if (bh >= n_streams) return;
+    const int b = bh / ka.Hkv, h = bh % ka.Hkv;
+    GlobalLogitSink<G> sink;
+#pragma unroll
+    for (int g = 0; g < G; ++g) sink.row[g] = logits + (size_t(b) * ka.Hq + size_t(h) * G + g) * (ka.T + 1);
+    sink.T = ka.T;
+    k_warp<BITS, G, EXACT>(ka, b, h, lane, kbuf[warp], kbar[warp], red[warp], sink);
+}
+
+template <int G>
+struct GlobalWeightSrc {
+    const __half *row[G];   // attention weights of each q head of this stream: [T+1]
+    float *wts;
+    __device__ __forceinline__ bool tile_weights(int i, int ntok, int lane, float (&)[G][4])
+    {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            wts[g * kTileTok + lane] = lane < ntok ? __half2float(row[g][i * kTileTok + lane]) : 0.f;
+        __syncwarp();
+        return true;
+    }
+    __device__ __forceinline__ bool self_weight(int, float (&)[G][4], float (&w_self)[G], int T)
+    {
+#pragma unroll
+        for (int g = 0; g < G; ++g) w_self[g] = __half2float(row[g][T]);
+        return true;
+    }
+    __device__ __forceinline__ float norm(int) const { return 1.f; }
+};
+
+template <int BITS, int G, bool EXACT>
+__global__ void __launch_bounds__(32 * kStreamsPerCta) forward_ov_kernel(VArgs va, const __half *__restrict__ attn,
+                                                                         int n_streams)
+{
+    __shared__ alignas(128) uint8_t vbuf[kStreamsPerCta][kStages * Tile<BITS>::BYTES];
+    __shared__ alignas(16) float wts[kStreamsPerCta][G * kTileTok];
+    __shared__ uint64_t vbar[kStreamsPerCta][kStages];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+        for (int i = 0; i < kStages; ++i) mbar_init(&vbar[warp][i], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const int bh = blockIdx.x * kStreamsPerCta + warp;
+    if (bh >= n_streams) return;
+    const int b = bh / va.Hkv, h = bh % va.Hkv;
+    GlobalWeightSrc<G> src;
+#pragma unroll
+    for (int g = 0; g < G; ++g) src.row[g] = attn + (size_t(b) * va.Hq + size_t(h) * G + g) * (va.T + 1);
+    src.wts = wts[warp];
+    v_warp<BITS, G, EXACT>(va, b, h, lane, vbuf[warp], vbar[warp], wts[warp], src);
+}
+
+}  // namespace adkv
+
+using namespace adkv;
+
+// Status word of this translation unit (read and cleared by adkv_device_status).
+ADKV_HIDDEN int adkv_tu_status_unfused(int *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
+    if (e != cudaSuccess) return int(e);
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+extern "C" {
+
+int adkv_forward_qk(const void *q, void *k_cache, const void *k_new, const adkv_params *p, void *logits, int B,
+                    int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scale_min, float scale_max,
+                    unsigned flags, void *stream)
+{
+    if (!q || !k_cache || !k_new || !logits || !params_ok(p)) return ADKV_E_NULL;
+    if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (!aligned16(k_cache) || !aligned8(q) || !aligned8(k_new) || !params_aligned(p)) return ADKV_E_ALIGN;
+    if (B == 0) return 0;
+    const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
+                   static_cast<const __half *>(k_new), to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+    const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    ADKV_DISPATCH(bits, exact, Hq / Hkv,
+                  (forward_qk_kernel<BITS, G, EXACT><<<grid, 32 * kStreamsPerCta, 0, s>>>(
+                      ka, static_cast<__half *>(logits), n_streams)))
+    return launch_status();
+}
+
+int adkv_forward_ov(const void *attn, void *v_cache, const void *v_new, const adkv_params *p, void *out, int B,
+                    int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scale_min, float scale_max,
+                    unsigned flags, void *stream)
+{
+    if (!attn || !v_cache || !v_new || !out || !params_ok(p)) return ADKV_E_NULL;
+    if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (!aligned16(v_cache) || !aligned8(out) || !aligned8(v_new) || !params_aligned(p)) return ADKV_E_ALIGN;
+    if (B == 0) return 0;
+    const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
+                   to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+    const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    ADKV_DISPATCH(bits, exact, Hq / Hkv,
+                  (forward_ov_kernel<BITS, G, EXACT><<<grid, 32 * kStreamsPerCta, 0, s>>>(
+                      va, static_cast<const __half *>(attn), n_streams)))
+    return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,96 @@
+"""Sharding plan and the N > 1 path on CPU (gloo, world size 2): per-rank results concatenate to the
+single-rank result, with no collective on the data path."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from adkv_b200 import sharding, synth
+from oracle import adkv_oracle as orc
+
+
+@pytest.mark.parametrize("B,Hkv,world", [(128, 32, 1), (128, 32, 2), (128, 32, 8), (32, 8, 8), (3, 8, 8),
+                                         (5, 3, 2), (1, 8, 4), (7, 1, 4)])
+def test_plan_covers_every_stream_once(B, Hkv, world):
+    shards = sharding.plan(B, Hkv, world)
+    assert [s.rank for s in shards] == list(range(world))
+    seen = np.zeros((B, Hkv), int)
+    for s in shards:
+        seen[s.b0:s.b1, s.h0:s.h1] += 1
+    assert (seen == 1).all()
+    sizes = [s.n_streams for s in shards]
+    assert max(sizes) - min(sizes) <= max(B, Hkv)          # balanced up to one row/column
+
+
+def test_plan_prefers_batch_split_and_rejects_impossible():
+    assert sharding.grid_for(128, 32, 8) == (8, 1)
+    assert sharding.grid_for(32, 8, 8) == (8, 1)
+    assert sharding.grid_for(4, 8, 8) == (4, 2)
+    with pytest.raises(ValueError):
+        sharding.plan(1, 2, 8)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, B, Hq, Hkv, T, bits, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    G, D = Hq // Hkv, 128
+    k = synth.gen_kv(1, B, Hkv, T + 1, D)
+    v = synth.gen_kv(2, B, Hkv, T + 1, D)
+    q = synth.gen_q(3, B, Hq, D)
+    kp, vp = synth.gen_params(4, Hkv, D, bits), synth.gen_params(5, Hkv, D, bits)
+    sh = sharding.plan(B, Hkv, world)[rank]
+    qs, ks, kps = sharding.take(sh, G, q=q, kv=k, params=kp)
+    vs, vps = sharding.take(sh, G, kv=v, params=vp)
+    npp = lambda p: tuple(t.float().numpy() for t in p)
+    ns = orc.n_super_for(T + 1, bits)
+    kc = np.zeros(orc.cache_shape(sh.b1 - sh.b0, sh.h1 - sh.h0, ns, D), np.uint8)
+    vc = np.zeros_like(kc)
+    orc.encode_kv(kc, ks[:, :, :T].numpy(), npp(kps), bits)
+    orc.encode_kv(vc, vs[:, :, :T].numpy(), npp(vps), bits)
+    out = orc.decode_attn(qs[:, :, 0].numpy(), kc, vc, ks[:, :, T].numpy(), vs[:, :, T].numpy(), npp(kps), npp(vps),
+                          T, 0.1, bits=bits)
+    # only the result hand-off is a collective; time is reduced with MAX as in the benchmark
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (sh, out))
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        full = np.zeros((B, Hq, D))
+        for s, o in gathered:
+            q0, q1 = s.q_heads(G)
+            full[s.b0:s.b1, q0:q1] = o
+        ret["full"], ret["tmax"] = full, t.item()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,bits", [(4, 4, 4, 4), (1, 8, 2, 2)])
+def test_two_ranks_concatenate_to_single_rank_result(B, Hq, Hkv, bits):
+    T, D, world = 37, 128, 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), B, Hq, Hkv, T, bits, ret), nprocs=world, join=True)
+    # single-rank reference
+    k = synth.gen_kv(1, B, Hkv, T + 1, D)
+    v = synth.gen_kv(2, B, Hkv, T + 1, D)
+    q = synth.gen_q(3, B, Hq, D)
+    npp = lambda p: tuple(t.float().numpy() for t in p)
+    kp, vp = npp(synth.gen_params(4, Hkv, D, bits)), npp(synth.gen_params(5, Hkv, D, bits))
+    ns = orc.n_super_for(T + 1, bits)
+    kc = np.zeros(orc.cache_shape(B, Hkv, ns, D), np.uint8)
+    vc = np.zeros_like(kc)
+    orc.encode_kv(kc, k[:, :, :T].numpy(), kp, bits)
+    orc.encode_kv(vc, v[:, :, :T].numpy(), vp, bits)
+    want = orc.decode_attn(q[:, :, 0].numpy(), kc, vc, k[:, :, T].numpy(), v[:, :, T].numpy(), kp, vp, T, 0.1, bits=bits)
+    assert np.array_equal(ret["full"], want)
+    assert ret["tmax"] == float(world)
