@@ -208,7 +208,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
@@ -224,13 +224,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns()
 }
 
 // Wait for a phase with a wall-clock limit (1 s).  Every lane of the calling warp must call it;
-// the result is warp-uniform.  On failure the status word records `code`.
+// the result is warp-uniform.  On failure the status word records `code`.  A warp that finds the
+// phase incomplete sleeps between polls so that it does not take issue slots from the warps it is
+// waiting for.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int code)
 {
     bool ok = mbar_try_wait(bar, parity);
     if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         for (uint32_t it = 1;; ++it) {
+            __nanosleep(it < 8 ? 128 : 512);
             ok = mbar_try_wait(bar, parity);
             if (ok) break;
             if ((it & 63u) == 0 && globaltimer_ns() - t0 > 1000000000ull) break;

@@ -54,7 +54,7 @@ def test_generation_across_growth_boundaries(bits, Hq, Hkv):
     for a, b, c in zip(o1, o2, o3):
         assert torch.equal(a, c)
         # the three-call sequence rounds logits and weights to fp16 as the reference does; the fused step does not
-            torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=3e-2 * float(a.abs().max()))
+        torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=3e-2 * float(a.abs().max()))
 
 
 def test_cache_object_errors_match_reference_behaviour():
