@@ -49,7 +49,12 @@ UNIT = "GB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
 # summarised under profiles/ (bytes); None where no capture exists for the workload.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # 273.1 MB measured on the batch-16 capture (profiles/decode_attn_kernel_4bit_b16_t4096.md); streams are
+    # independent, so traffic scales with the batch: x8 for batch 128
+    "config2_llama2_7b_b128_t4096_4bit": 8 * 273_142_784,
+    "profile_b16_t4096_4bit": 273_142_784,
+}
 
 
 def algorithmic_bytes(w) -> int:
