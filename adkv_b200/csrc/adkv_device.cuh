@@ -123,16 +123,16 @@ __device__ __forceinline__ float replay_step(float q, Chan &c, float smin, float
 
 // Interval of scales from which 8 further updates cannot leave [max(smin, eps), smax]: inside it the
 // clamp and the eps guard are the identity and the unguarded step gives bit-identical results.
-// One conservative interval per lane (intersection over its 4 channels).
+// One conservative interval per lane (intersection over its channels).
 struct SafeRange {
     float lo, hi;
-    template <int BITS>
-    __device__ __forceinline__ void init(const float (&beta)[4], const float (&target)[4], float smin, float smax)
+    template <int BITS, int N>
+    __device__ __forceinline__ void init(const float (&beta)[N], const float (&target)[N], float smin, float smax)
     {
         lo = 0.f;
         hi = INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < N; ++c) {
             const float g0 = 1.f - beta[c] * target[c];                      // |q| = 0
             const float g1 = g0 + beta[c] * float(Codec<BITS>::BIAS);        // |q| = largest code magnitude
             const float gmn = fminf(fminf(g0, g1), 1.f), gmx = fmaxf(fmaxf(g0, g1), 1.f);
@@ -153,6 +153,10 @@ struct SafeRange {
         const float mx = fmaxf(fmaxf(ch[0].s, ch[1].s), fmaxf(ch[2].s, ch[3].s));
         return __all_sync(kFull, mn >= lo && mx <= hi);
     }
+    __device__ __forceinline__ bool holds(const Chan (&ch)[2]) const
+    {
+        return __all_sync(kFull, fminf(ch[0].s, ch[1].s) >= lo && fmaxf(ch[0].s, ch[1].s) <= hi);
+    }
 };
 
 // Encoder side of one token, canonical order only (train_model.py:72, :8-17).  Returns the
@@ -165,6 +169,39 @@ __device__ __forceinline__ float quantize(float x, const Chan &c, float &rh)
     const float q = fminf(fmaxf(rintf(v), Codec<BITS>::qlo()), Codec<BITS>::qhi());
     rh = __fmul_rn(q, ss);
     return q;
+}
+
+// Speculative form of quantize(): the quotient is formed with the approximate reciprocal (error
+// below 2.2e-6 for |v| < 16) and rounded with the 1.5*2^23 trick after clamping (clamp and
+// round-to-nearest-even commute because the limits are integers).  The result equals the canonical
+// one unless the approximate quotient lies within 4e-6 of a rounding boundary k + 0.5; that case
+// sets `doubt`, and the caller redoes the tokens with quantize() from a saved state.  No branch
+// sits on the token-to-token dependency chain.  `tbits` carries the code in its low bits:
+// field = (tbits & FIELD) ^ BIAS.  GUARDED as in replay_step.
+template <int BITS, bool GUARDED>
+__device__ __forceinline__ float quantize_spec(float x, const Chan &c, float &rh, uint32_t &tbits, bool &doubt)
+{
+    constexpr float M = 12582912.f;   // 1.5 * 2^23
+    const float ss = GUARDED ? fmaxf(c.s, kEps) : c.s;
+    const float r = __fsub_rn(x, c.zp);
+    float inv;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(ss));
+    const float v = __fmul_rn(r, inv);
+    const float t = __fadd_rn(fminf(fmaxf(v, Codec<BITS>::qlo()), Codec<BITS>::qhi()), M);
+    const float q = __fsub_rn(t, M);
+    doubt |= !(fabsf(fabsf(__fsub_rn(v, q)) - 0.5f) > 4e-6f);
+    rh = __fmul_rn(q, ss);
+    tbits = __float_as_uint(t);
+    return q;
+}
+
+template <bool GUARDED>
+__device__ __forceinline__ void advance_canonical_g(float q, float rh, Chan &c, float smin, float smax)
+{
+    c.zp = __fadd_rn(c.zp, __fmul_rn(c.alpha, rh));
+    const float err = __fsub_rn(fabsf(q), c.tc);
+    const float s_new = __fadd_rn(c.s, __fmul_rn(__fmul_rn(c.s, c.beta), err));
+    c.s = GUARDED ? fminf(fmaxf(s_new, smin), smax) : s_new;
 }
 
 __device__ __forceinline__ void advance_canonical(float q, float rh, Chan &c, float smin, float smax)
@@ -295,7 +332,7 @@ __device__ __forceinline__ void load_chan4(Chan (&ch)[4], SafeRange &safe, const
         beta[2 * i] = be.x; beta[2 * i + 1] = be.y;
         target[2 * i] = tg.x; target[2 * i + 1] = tg.y;
     }
-    safe.init<BITS>(beta, target, smin, smax);
+    safe.template init<BITS, 4>(beta, target, smin, smax);
 }
 
 __device__ __forceinline__ void load_half4(float (&v)[4], const __half *p)

@@ -5,84 +5,145 @@
 namespace adkv {
 
 // =========================================================================================
-// Prefill quantise + pack (canonical arithmetic).  One CTA per (batch, head), one thread per
-// channel: the warp reads 64 contiguous bytes of a token row and writes 128 contiguous bytes
-// of a supergroup.  The next word's tokens are fetched while the current word is quantised.
-template <int BITS>
-__global__ void __launch_bounds__(kD) encode_kernel(uint32_t *__restrict__ cache, const __half *__restrict__ x,
-                                                    ParamPtrs p, float *__restrict__ tail, int H, int T,
-                                                    int n_super_cap, int t_start, float smin, float smax)
+// Prefill quantise + pack (canonical arithmetic).  One 64-thread CTA per (batch, head); a thread
+// owns two adjacent channels: per token the warp reads 128 contiguous bytes of the fp16 row
+// (half2 per lane) and per supergroup it writes 256 contiguous bytes (uint2 per lane).  The next
+// word's tokens are fetched while the current word is quantised.
+constexpr int kEncThreads = kD / 2;
+
+// Eight tokens (fields J0 .. J0+7 of the word being assembled) for the two channels of a thread,
+// speculative quantiser; returns true when some code is in doubt and the group must be redone.
+template <int BITS, bool GUARDED, int J0>
+__device__ __forceinline__ bool encode_group(const __half2 (&xin)[8], Chan (&ch)[2], uint32_t (&word)[2],
+                                             float smin, float smax)
 {
     using C = Codec<BITS>;
-    const int bh = blockIdx.x, h = bh % H, c = threadIdx.x;
-    const size_t po = size_t(h) * kD + c;
-    Chan ch;
-    ch.alpha = __half2float(p.alpha[po]);
-    ch.beta = __half2float(p.beta[po]);
-    ch.tc = __half2float(p.target[po]);
-    if (t_start > 0) {
-        ch.zp = tail[size_t(bh) * 2 * kD + c];
-        ch.s = tail[size_t(bh) * 2 * kD + kD + c];
-    } else {
-        ch.zp = __half2float(p.zp_init[po]);
-        ch.s = __half2float(p.scale_init[po]);
+    bool doubt = !(ch[0].s < 1e29f) || !(ch[1].s < 1e29f);   // reciprocal would flush to zero
+    static_for<8>([&](auto jc) {
+        constexpr int j = decltype(jc)::value;
+        const float2 x = __half22float2(xin[j]);
+        const float xs[2] = {x.x, x.y};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float rh;
+            uint32_t tb;
+            const float q = quantize_spec<BITS, GUARDED>(xs[c], ch[c], rh, tb, doubt);
+            advance_canonical_g<GUARDED>(q, rh, ch[c], smin, smax);
+            word[c] |= ((tb & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
+        }
+    });
+    return doubt;
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kEncThreads) encode_kernel(uint32_t *__restrict__ cache,
+                                                             const __half *__restrict__ x, ParamPtrs p,
+                                                             float *__restrict__ tail, int H, int T, int n_super_cap,
+                                                             int t_start, float smin, float smax)
+{
+    using C = Codec<BITS>;
+    const int bh = blockIdx.x, h = bh % H, c0 = 2 * threadIdx.x;
+    const size_t po = size_t(h) * kD + c0;
+    Chan ch[2];
+    float beta[2], target[2];
+    {
+        const float2 al = __half22float2(*reinterpret_cast<const __half2 *>(p.alpha + po));
+        const float2 be = __half22float2(*reinterpret_cast<const __half2 *>(p.beta + po));
+        const float2 tg = __half22float2(*reinterpret_cast<const __half2 *>(p.target + po));
+        float2 zp, sc;
+        if (t_start > 0) {
+            zp = *reinterpret_cast<const float2 *>(tail + size_t(bh) * 2 * kD + c0);
+            sc = *reinterpret_cast<const float2 *>(tail + size_t(bh) * 2 * kD + kD + c0);
+        } else {
+            zp = __half22float2(*reinterpret_cast<const __half2 *>(p.zp_init + po));
+            sc = __half22float2(*reinterpret_cast<const __half2 *>(p.scale_init + po));
+        }
+        ch[0] = Chan{zp.x, sc.x, al.x, be.x, tg.x};
+        ch[1] = Chan{zp.y, sc.y, al.y, be.y, tg.y};
+        beta[0] = be.x; beta[1] = be.y; target[0] = tg.x; target[1] = tg.y;
     }
-    uint32_t *w = cache + size_t(bh) * n_super_cap * kD + c;
-    const __half *xs = x + size_t(bh) * T * kD + c;   // token t_start + i is row i
+    SafeRange safe;
+    safe.template init<BITS, 2>(beta, target, smin, smax);
+
+    uint2 *w = reinterpret_cast<uint2 *>(cache + size_t(bh) * n_super_cap * kD + c0);       // stride kD/2 per word row
+    const __half2 *xs = reinterpret_cast<const __half2 *>(x + size_t(bh) * T * kD + c0);    // stride kD/2 per token
+    constexpr int RS = kD / 2;
+
+    // one token with a run-time field position, exactly rounded division (partial words, redone groups)
+    auto exact_token = [&](int t, uint32_t(&word)[2]) {
+        const float2 xv = __half22float2(xs[size_t(t - t_start) * RS]);
+        const float xa[2] = {xv.x, xv.y};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float rh;
+            const float q = quantize<BITS>(xa[c], ch[c], rh);
+            word[c] |= uint32_t(int(q) + C::BIAS) << (BITS * (t % C::TPW));
+            advance_canonical(q, rh, ch[c], smin, smax);
+        }
+    };
 
     const int t_end = t_start + T;
     int t = t_start;
-    // leading partial word (chunked prefill that starts inside a word)
+    uint32_t word[2] = {0u, 0u};
+    // a chunk that starts inside a word keeps the fields already there
     if (t % C::TPW != 0 && t < t_end) {
-        const int sg = t / C::TPW;
-        uint32_t word = w[size_t(sg) * kD] & ((1u << (BITS * (t % C::TPW))) - 1u);
-        for (; t < t_end && t / C::TPW == sg; ++t) {
-            float rh;
-            const float q = quantize<BITS>(__half2float(xs[size_t(t - t_start) * kD]), ch, rh);
-            word |= uint32_t(int(q) + C::BIAS) << (BITS * (t % C::TPW));
-            advance_canonical(q, rh, ch, smin, smax);
-        }
-        w[size_t(sg) * kD] = word;
+        const uint2 old = w[size_t(t / C::TPW) * RS];
+        const uint32_t keep = (1u << (BITS * (t % C::TPW))) - 1u;
+        word[0] = old.x & keep;
+        word[1] = old.y & keep;
     }
-    // full words, software-pipelined loads
-    __half cur[C::TPW], nxt[C::TPW];
-    const int n_full = (t_end - t) / C::TPW;
-    if (n_full > 0) {
-#pragma unroll
-        for (int j = 0; j < C::TPW; ++j) cur[j] = xs[size_t(t - t_start + j) * kD];
-    }
-    for (int i = 0; i < n_full; ++i, t += C::TPW) {
-        if (i + 1 < n_full) {
-#pragma unroll
-            for (int j = 0; j < C::TPW; ++j) nxt[j] = xs[size_t(t - t_start + C::TPW + j) * kD];
+    // tokens up to the next multiple of 8
+    for (; t < t_end && t % 8 != 0; ++t) {
+        exact_token(t, word);
+        if ((t + 1) % C::TPW == 0) {
+            w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
+            word[0] = word[1] = 0u;
         }
-        uint32_t word = 0;
-#pragma unroll
-        for (int j = 0; j < C::TPW; ++j) {
-            float rh;
-            const float q = quantize<BITS>(__half2float(cur[j]), ch, rh);
-            word |= uint32_t(int(q) + C::BIAS) << (BITS * j);
-            advance_canonical(q, rh, ch, smin, smax);
-        }
-        w[size_t(t / C::TPW) * kD] = word;
-#pragma unroll
-        for (int j = 0; j < C::TPW; ++j) cur[j] = nxt[j];
     }
-    // trailing partial word: unused fields stay zero
-    if (t < t_end) {
-        const int sg = t / C::TPW;
-        uint32_t word = 0;
-        for (; t < t_end; ++t) {
-            float rh;
-            const float q = quantize<BITS>(__half2float(xs[size_t(t - t_start) * kD]), ch, rh);
-            word |= uint32_t(int(q) + C::BIAS) << (BITS * (t % C::TPW));
-            advance_canonical(q, rh, ch, smin, smax);
-        }
-        w[size_t(sg) * kD] = word;
+    // groups of 8 tokens, loads of the next group in flight while the current one is quantised
+    const int n_groups = (t_end - t) / 8;
+    __half2 cur[8], nxt[8];
+    if (n_groups > 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = xs[size_t(t - t_start + j) * RS];
     }
+#pragma unroll 1
+    for (int g = 0; g < n_groups; ++g, t += 8) {
+        if (g + 1 < n_groups) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) nxt[j] = xs[size_t(t - t_start + 8 + j) * RS];
+        }
+        const Chan saved[2] = {ch[0], ch[1]};
+        const uint32_t word_in[2] = {word[0], word[1]};
+        const bool second = C::TPW == 16 && (t & 8);
+        bool doubt;
+        if (safe.holds(ch)) {
+            doubt = second ? encode_group<BITS, false, 8 % C::TPW>(cur, ch, word, smin, smax)
+                           : encode_group<BITS, false, 0>(cur, ch, word, smin, smax);
+        } else {
+            doubt = second ? encode_group<BITS, true, 8 % C::TPW>(cur, ch, word, smin, smax)
+                           : encode_group<BITS, true, 0>(cur, ch, word, smin, smax);
+        }
+        if (doubt) {   // rare, per thread: redo the group from the saved state with the exact quantiser
+            ch[0] = saved[0];
+            ch[1] = saved[1];
+            word[0] = word_in[0];
+            word[1] = word_in[1];
+            for (int j = 0; j < 8; ++j) exact_token(t + j, word);
+        }
+        if ((t + 8) % C::TPW == 0) {
+            w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
+            word[0] = word[1] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+    }
+    // trailing tokens; unused fields of the last word stay zero
+    for (; t < t_end; ++t) exact_token(t, word);
+    if (t % C::TPW != 0) w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
     if (tail) {
-        tail[size_t(bh) * 2 * kD + c] = ch.zp;
-        tail[size_t(bh) * 2 * kD + kD + c] = ch.s;
+        *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * kD + c0) = make_float2(ch[0].zp, ch[1].zp);
+        *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * kD + kD + c0) = make_float2(ch[0].s, ch[1].s);
     }
 }
 
@@ -124,14 +185,19 @@ int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, in
     if (t_start < 0) return ADKV_E_SHAPE;
     if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
     if (t_start > 0 && !tail) return ADKV_E_START;
+    if ((reinterpret_cast<uintptr_t>(cache) & 7u) || (reinterpret_cast<uintptr_t>(x) & 3u) ||
+        (reinterpret_cast<uintptr_t>(tail) & 7u) || (reinterpret_cast<uintptr_t>(p->zp_init) & 3u) ||
+        (reinterpret_cast<uintptr_t>(p->scale_init) & 3u) || (reinterpret_cast<uintptr_t>(p->alpha) & 3u) ||
+        (reinterpret_cast<uintptr_t>(p->beta) & 3u) || (reinterpret_cast<uintptr_t>(p->target) & 3u))
+        return ADKV_E_ALIGN;
     if (B * H == 0 || (T == 0 && !(tail && t_start == 0))) return 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (bits == 4)
-        encode_kernel<4><<<B * H, kD, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x),
+        encode_kernel<4><<<B * H, kEncThreads, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x),
                                               to_ptrs(p), static_cast<float *>(tail), H, T, n_super_cap, t_start,
                                               scale_min, scale_max);
     else
-        encode_kernel<2><<<B * H, kD, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x),
+        encode_kernel<2><<<B * H, kEncThreads, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x),
                                               to_ptrs(p), static_cast<float *>(tail), H, T, n_super_cap, t_start,
                                               scale_min, scale_max);
     return launch_status();

@@ -39,6 +39,11 @@ WORKLOADS = {
     "config2_llama2_7b_b128_t4096_4bit": dict(B=128, Hq=32, Hkv=32, D=128, T=4096, bits=4),
     "config5_llama3_8b_gqa_b32_t32768_2bit": dict(B=32, Hq=32, Hkv=8, D=128, T=32768, bits=2),
     "small_b8_t1024_4bit": dict(B=8, Hq=32, Hkv=32, D=128, T=1024, bits=4),
+    # prefill quantise of one layer's K and V (config 3 has 32 such layers), then single-token appends
+    "config3_prefill_b16_t8192_4bit": dict(kind="encode", B=16, Hq=32, Hkv=32, D=128, T=8192, bits=4, appends=256),
+    "config3_prefill_b16_t8192_2bit": dict(kind="encode", B=16, Hq=32, Hkv=32, D=128, T=8192, bits=2, appends=256),
+    "profile_prefill_b16_t2048_4bit": dict(kind="encode", B=16, Hq=32, Hkv=32, D=128, T=2048, bits=4, appends=8),
+    "profile_prefill_b16_t2048_2bit": dict(kind="encode", B=16, Hq=32, Hkv=32, D=128, T=2048, bits=2, appends=8),
     # profiling-sized cases: same kernels and per-stream work, a few hundred MB on the device
     "profile_b16_t4096_4bit": dict(B=16, Hq=32, Hkv=32, D=128, T=4096, bits=4),
     "profile_gqa_b8_t16384_2bit": dict(B=8, Hq=32, Hkv=8, D=128, T=16384, bits=2),
@@ -58,8 +63,11 @@ NCU_TRAFFIC_BYTES = {
 
 
 def algorithmic_bytes(w) -> int:
-    """Bytes one decode step must move: packed K and V, q and out, k_new and v_new, parameters."""
+    """Bytes one step must move.  Decode: packed K and V, q and out, k_new and v_new, parameters.
+    Encode (prefill quantise of K and V): fp16 in, packed codes out."""
     B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
+    if w.get("kind") == "encode":
+        return 2 * (B * Hkv * T * D * 2 + B * Hkv * T * D * bits // 8)
     return 2 * B * Hkv * T * D * bits // 8 + 2 * B * Hq * D * 2 + 2 * B * Hkv * D * 2 + 10 * Hkv * D * 2
 
 
@@ -285,6 +293,124 @@ def check_against_oracle(w, st, out, n_streams, torch):
     return ok, dt, n_streams, c_oracle.num_threads()
 
 
+def run_encode(args, w, name):
+    """Prefill-quantise workload: a step encodes one layer's K and V (two launches of encode_kernel)."""
+    import numpy as np
+    import torch
+
+    from adkv_b200 import gemv, synth
+    from oracle import c_oracle
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == 1, "the prefill workload is a single-GPU measurement"
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    B, H, D, T, bits = w["B"], w["Hkv"], w["D"], w["T"], w["bits"]
+    kp = synth.gen_params(3, H, D, bits, device=device)
+    vp = synth.gen_params(4, H, D, bits, device=device)
+    k = torch.cat([synth.gen_kv(10 + b, 1, H, T, D, device=device) for b in range(B)])
+    v = torch.cat([synth.gen_kv(110 + b, 1, H, T, D, device=device) for b in range(B)])
+    ns = gemv.n_super_for(T + w["appends"], bits)
+    kc = torch.zeros((B, H, ns, D // 4, 4, 4), dtype=torch.uint8, device=device)
+    vc = torch.zeros_like(kc)
+    tk = torch.empty((B, H, 2, D), dtype=torch.float32, device=device)
+    tv = torch.empty_like(tk)
+
+    def step(ks=k, vs=v):
+        gemv.encode_kv(kc, ks, *kp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, tail=tk)
+        gemv.encode_kv(vc, vs, *vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, tail=tv)
+
+    prop = torch.cuda.get_device_properties(device)
+    try:
+        bus_id = f"{prop.pci_domain_id:08x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+    except AttributeError:
+        bus_id = None
+    sampler = ClockSampler(local, bus_id)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(device)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    t0 = time.perf_counter()
+    ev[0].record()
+    for i in range(args.steps):
+        step()
+        ev[i + 1].record()
+    torch.cuda.synchronize(device)
+    t1 = time.perf_counter()
+    sampler.stop()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+
+    # single-token appends from the persisted tail state (K and V: two launches per appended token)
+    kn = synth.gen_kv(5, B, H, w["appends"], D, device=device, pos0=T)
+    vn = synth.gen_kv(6, B, H, w["appends"], D, device=device, pos0=T)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for i in range(w["appends"]):
+        gemv.append_kv(kc, kn[:, :, i:i + 1], *kp, tk, T + i, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+        gemv.append_kv(vc, vn[:, :, i:i + 1], *vp, tv, T + i, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+    a1.record()
+    torch.cuda.synchronize(device)
+    append_us = a0.elapsed_time(a1) * 1e3 / w["appends"]
+
+    # end to end: fp16 K/V from pinned host memory every step, tail states read back
+    hk, hv = k.cpu().pin_memory(), v.cpu().pin_memory()
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    htail = torch.empty_like(tk, device="cpu").pin_memory()
+    e2e_steps = max(1, min(args.steps, 5))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(1 + e2e_steps):
+        if it == 1:
+            e0.record()
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        step(dk, dv)
+        htail.copy_(tk, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize(device)
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # CPU restatement on a bounded sample of sequences; also checks the GPU's codes for them
+    nb = 1
+    kc_cpu = np.zeros((nb, H, ns, D // 4, 4, 4), np.uint8)
+    xk = hk[:nb].numpy()
+    f = lambda ps: tuple(p.float().cpu().numpy() for p in ps)
+    c_oracle.encode(kc_cpu, xk, f(kp), bits, synth.SCALE_MIN, synth.SCALE_MAX)
+    tc0 = time.perf_counter()
+    c_oracle.encode(kc_cpu, xk, f(kp), bits, synth.SCALE_MIN, synth.SCALE_MAX)
+    cpu_dt = time.perf_counter() - tc0
+    step()
+    used = gemv.n_super_for(T, bits)
+    ok = np.array_equal(kc[:nb, :, :used].cpu().numpy(), kc_cpu[:, :, :used])
+
+    nbytes = algorithmic_bytes(w)
+    peak, peak_src = measured_peak_gbs()
+    avg_ms = sum(per_step) / len(per_step)
+    res = {
+        "metric": "adkv_prefill_quantize_bandwidth", "value": nbytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": dict(workload=name, per_gpu=w, l2="inputs larger than L2; no flush needed"),
+        "e2e": {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * k.numel() * 2,
+                "d2h_bytes_per_step": htail.numel() * 4, "ms_per_step": e2e_ms},
+        "gpu_launches": 2 * args.steps,
+        "append_us_per_token_kv": append_us,
+        "roofline": {"bound": "hbm", "achieved": nbytes / (avg_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": nbytes / (avg_ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
+                     "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel": "encode_kernel (2 launches per step)",
+                     "algorithmic_bytes_per_step": nbytes, "avg_step_ms": avg_ms},
+        "clocks": sampler.summary(t0, t1),
+        "cpu_baseline": {"value": nb * H * T * D * (2 + bits / 8) / cpu_dt / 1e9, "unit": UNIT,
+                         "cores": c_oracle.num_threads(), "kind": "port", "seconds": cpu_dt,
+                         "sample": f"K of {nb} of {B} sequences ({nb * H} streams), C restatement with OpenMP"},
+        "parity_check": "ok" if ok else "FAILED",
+    }
+    print(json.dumps(res), flush=True)
+    if not ok:
+        sys.exit(1)
+
+
 def run_ours(args, w, name):
     import torch
     import torch.distributed as dist
@@ -437,6 +563,8 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, w, args.workload)
+    elif w.get("kind") == "encode":
+        run_encode(args, w, args.workload)
     else:
         run_ours(args, w, args.workload)
 

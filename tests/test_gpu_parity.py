@@ -272,6 +272,66 @@ def test_full_size_config2_properties():
             assert dmax <= 1 and frac <= 1e-4
 
 
+def test_full_size_config5_gqa_2bit_properties():
+    """BASELINE config 5 shape (B 32, 32 q heads over 8 KV heads, T 32768, 2-bit): one distinct sequence
+    replicated over the batch; every replica must reproduce the oracle's result and appended codes."""
+    B, Hq, Hkv, T, bits, D = 32, 32, 8, 32768, 2, 128
+    from oracle import c_oracle
+    case = make_case(901, 1, Hq, Hkv, T, bits)
+    ns = orc.n_super_for(T + 1, bits)
+    kc = np.zeros(orc.cache_shape(1, Hkv, ns, D), np.uint8)
+    vc = np.zeros_like(kc)
+    c_oracle.encode(kc, case["k"][:, :, :T].numpy(), np_params(case["kp"]), bits, SMIN, SMAX)
+    c_oracle.encode(vc, case["v"][:, :, :T].numpy(), np_params(case["vp"]), bits, SMIN, SMAX)
+    rep = lambda t: dev(t).repeat(B, *([1] * (t.dim() - 1)))
+    dk = torch.zeros(orc.cache_shape(B, Hkv, ns, D), dtype=torch.uint8, device="cuda")
+    dv = torch.zeros_like(dk)
+    gemv.encode_kv(dk, rep(case["k"][:, :, :T]), *dev(case["kp"]), SMIN, SMAX, bits=bits)
+    gemv.encode_kv(dv, rep(case["v"][:, :, :T]), *dev(case["vp"]), SMIN, SMAX, bits=bits)
+    assert np.array_equal(dk[:1].cpu().numpy(), kc) and np.array_equal(dv[-1:].cpu().numpy(), vc)
+    scaling = D ** -0.5
+    want = c_oracle.decode_attn(case["q"][:, :, 0].numpy(), kc, vc, case["k"][:, :, T].numpy(),
+                                case["v"][:, :, T].numpy(), np_params(case["kp"]), np_params(case["vp"]),
+                                T, scaling, bits, SMIN, SMAX)
+    out = gemv.decode_attn(rep(case["q"]), dk, dv, rep(case["k"][:, :, T:T + 1]), rep(case["v"][:, :, T:T + 1]),
+                           dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits)
+    _status_ok()
+    got = out.float().cpu().numpy()
+    assert np.array_equal(got, np.broadcast_to(got[:1], got.shape))
+    np.testing.assert_allclose(got[:1], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    assert np.array_equal(dk[:1].cpu().numpy(), kc) and np.array_equal(dv[-1:].cpu().numpy(), vc)
+    assert torch.equal(dk[0], dk[-1]) and torch.equal(dv[0], dv[-1])
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_full_size_config3_prefill_properties(bits):
+    """BASELINE config 3 shape for one layer (B 16, H 32, T 8192): 2 distinct sequences replicated; every
+    replica equals the oracle's codes and tail state; encoding in three chunks and appending the last 256
+    tokens one by one gives the same cache as the one-shot prefill."""
+    B, H, T, D, R, A = 16, 32, 8192, 128, 2, 256
+    from oracle import c_oracle
+    x = synth.gen_kv(902 + bits, R, H, T + A, D)
+    p = synth.gen_params(903, H, D, bits)
+    ns = orc.n_super_for(T + A, bits)
+    want = np.zeros(orc.cache_shape(R, H, ns, D), np.uint8)
+    tail_want = c_oracle.encode(want, x.numpy(), np_params(p), bits, SMIN, SMAX, want_tail=True)
+    xd = dev(x).repeat(B // R, 1, 1, 1)
+    pd = dev(p)
+    one = torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    t_one = torch.empty(B, H, 2, D, dtype=torch.float32, device="cuda")
+    gemv.encode_kv(one, xd, *pd, SMIN, SMAX, bits=bits, tail=t_one)
+    assert np.array_equal(one[:R].cpu().numpy(), want) and torch.equal(one[:R], one[-R:])
+    assert np.array_equal(t_one[:R].cpu().numpy().view(np.uint32), tail_want.view(np.uint32))
+    parts = torch.zeros_like(one)
+    t_parts = torch.empty_like(t_one)
+    cuts = [0, 1000, 4099, T]                       # chunk boundaries inside words
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        gemv.encode_kv(parts, xd[:, :, a:b].contiguous(), *pd, SMIN, SMAX, bits=bits, tail=t_parts, t_start=a)
+    for t in range(T, T + A):
+        gemv.append_kv(parts, xd[:, :, t:t + 1].contiguous(), *pd, t_parts, t, SMIN, SMAX, bits=bits)
+    assert torch.equal(parts, one) and torch.equal(t_parts.view(torch.int32), t_one.view(torch.int32))
+
+
 # ------------------------------------------------------------------------------- errors
 
 def test_argument_errors_raise_runtime_error():
