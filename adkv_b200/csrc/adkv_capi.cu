@@ -4,6 +4,7 @@
 
 ADKV_HIDDEN int adkv_tu_status_fused(int *out);
 ADKV_HIDDEN int adkv_tu_status_unfused(int *out);
+ADKV_HIDDEN int adkv_tu_status_encode(int *out);
 
 extern "C" {
 
@@ -29,10 +30,11 @@ int adkv_device_status(int *status, void *stream)
     if (!status) return ADKV_E_NULL;
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return int(e);
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     if (int rc = adkv_tu_status_fused(&a)) return rc;
     if (int rc = adkv_tu_status_unfused(&b)) return rc;
-    *status = a ? a : b;
+    if (int rc = adkv_tu_status_encode(&c)) return rc;
+    *status = a ? a : (b ? b : c);
     return 0;
 }
 

@@ -81,8 +81,9 @@ struct StreamRing {
 
 // ---------------------------------------------------------------------------------- K side
 
-// Replay 8 tokens (fields J0..J0+7 of the 4 words in `w`) and accumulate the partial dot products.
-template <int BITS, int G, bool EXACT, int J0, bool PARTIAL, bool GUARDED>
+// Replay 8 tokens (fields 0..7 of the 4 words in `w`; the caller shifts the second half of a 16-token
+// word down) and accumulate the partial dot products.  `count`: valid fields when PARTIAL.
+template <int BITS, int G, bool EXACT, bool PARTIAL, bool GUARDED>
 __device__ __forceinline__ void k_chunk(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
                                         const float (&qv)[G][4], float (&part)[G][8], int count, float smin,
                                         float smax)
@@ -91,21 +92,22 @@ __device__ __forceinline__ void k_chunk(const uint4 &w, const FieldConsts<BITS> 
     uint32_t lo[4], hi[4];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        lo[c] = field_group<BITS, J0>(ww[c]);
-        hi[c] = field_group<BITS, J0 + 4>(ww[c]);
+        lo[c] = ww[c];
+        hi[c] = ww[c] >> (4 * BITS);
     }
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
-#pragma unroll
-        for (int g = 0; g < G; ++g) part[g][j] = 0.f;
-        if (!PARTIAL || J0 + j < count) {
+        if (!PARTIAL || j < count) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float q = fc.template code<j % 4>(j < 4 ? lo[c] : hi[c]);
                 const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
 #pragma unroll
-                for (int g = 0; g < G; ++g) part[g][j] = fmaf(qv[g][c], xh, part[g][j]);
+                for (int g = 0; g < G; ++g) part[g][j] = c == 0 ? qv[g][0] * xh : fmaf(qv[g][c], xh, part[g][j]);
             }
+        } else {
+#pragma unroll
+            for (int g = 0; g < G; ++g) part[g][j] = 0.f;
         }
     });
 }
@@ -181,34 +183,29 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
 #pragma unroll 1
             for (int wd = 0; wd < Tile<BITS>::WORDS; ++wd) {
                 const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
-#pragma unroll
+#pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
-                    if (safe.holds(ch)) {
-                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, false>(w, fc, ch, qv, part, 8, a.smin, a.smax);
-                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, fc, ch, qv, part, 8, a.smin, a.smax);
-                    } else {
-                        if (c8 == 0) k_chunk<BITS, G, EXACT, 0, false, true>(w, fc, ch, qv, part, 8, a.smin, a.smax);
-                        else k_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, fc, ch, qv, part, 8, a.smin, a.smax);
-                    }
+                    if (safe.holds(ch)) k_chunk<BITS, G, EXACT, false, false>(w, fc, ch, qv, part, 8, a.smin, a.smax);
+                    else k_chunk<BITS, G, EXACT, false, true>(w, fc, ch, qv, part, 8, a.smin, a.smax);
                     reduce8<G>(part, red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
+                    if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }
                 w = w_next;
             }
         } else {
 #pragma unroll 1
             for (int wd = 0; wd * C::TPW < ntok; ++wd) {
-                const uint4 w = tile[wd * (kD / 4)];
+                uint4 w = tile[wd * (kD / 4)];
                 const int count = ntok - wd * C::TPW;   // valid fields in this word (may exceed TPW)
-#pragma unroll
-                for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
-                    if (c8 * 8 >= count) break;
-                    if (c8 == 0) k_chunk<BITS, G, EXACT, 0, true, true>(w, fc, ch, qv, part, count, a.smin, a.smax);
-                    else k_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, fc, ch, qv, part, count, a.smin, a.smax);
+#pragma unroll 1
+                for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
+                    k_chunk<BITS, G, EXACT, true, true>(w, fc, ch, qv, part, count - c8 * 8, a.smin, a.smax);
                     reduce8<G>(part, red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
+                    if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }
             }
         }
@@ -250,7 +247,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
 
 // ---------------------------------------------------------------------------------- V side
 
-template <int BITS, int G, bool EXACT, int J0, bool PARTIAL, bool GUARDED>
+template <int BITS, int G, bool EXACT, bool PARTIAL, bool GUARDED>
 __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
                                         const float *wts /* [G][32] smem */, int tok0, float (&acc)[G][4],
                                         int count, float smin, float smax)
@@ -259,8 +256,8 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> 
     uint32_t lo[4], hi[4];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        lo[c] = field_group<BITS, J0>(ww[c]);
-        hi[c] = field_group<BITS, J0 + 4>(ww[c]);
+        lo[c] = ww[c];
+        hi[c] = ww[c] >> (4 * BITS);
     }
     float wt[G][8];
 #pragma unroll
@@ -272,7 +269,7 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> 
     }
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
-        if (!PARTIAL || J0 + j < count) {
+        if (!PARTIAL || j < count) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float q = fc.template code<j % 4>(j < 4 ? lo[c] : hi[c]);
@@ -332,28 +329,26 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
 #pragma unroll 1
             for (int wd = 0; wd < Tile<BITS>::WORDS; ++wd) {
                 const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
-#pragma unroll
+#pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     const int tok0 = wd * C::TPW + c8 * 8;
-                    if (safe.holds(ch)) {
-                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, false>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
-                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, false>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
-                    } else {
-                        if (c8 == 0) v_chunk<BITS, G, EXACT, 0, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
-                        else v_chunk<BITS, G, EXACT, 8 % C::TPW, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
-                    }
+                    if (safe.holds(ch)) v_chunk<BITS, G, EXACT, false, false>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                    else v_chunk<BITS, G, EXACT, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                    if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }
                 w = w_next;
             }
         } else {
 #pragma unroll 1
             for (int wd = 0; wd * C::TPW < ntok; ++wd) {
-                const uint4 w = tile[wd * (kD / 4)];
+                uint4 w = tile[wd * (kD / 4)];
                 const int count = ntok - wd * C::TPW;
-                v_chunk<BITS, G, EXACT, 0, true, true>(w, fc, ch, wts, wd * C::TPW, acc, count, a.smin, a.smax);
-                if (C::TPW == 16 && count > 8)
-                    v_chunk<BITS, G, EXACT, 8 % C::TPW, true, true>(w, fc, ch, wts, wd * C::TPW + 8, acc, count, a.smin,
-                                                                    a.smax);
+#pragma unroll 1
+                for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
+                    v_chunk<BITS, G, EXACT, true, true>(w, fc, ch, wts, wd * C::TPW + c8 * 8, acc, count - c8 * 8,
+                                                        a.smin, a.smax);
+                    if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
+                }
             }
         }
         ring.release_and_refill(i, lane);   // also orders this tile's reads of wts before the next fill

@@ -78,13 +78,6 @@ struct FieldConsts {
     }
 };
 
-// Field J (0..TPW-1) of word w: group J/4 shifted to bit 0.
-template <int BITS, int J>
-__device__ __forceinline__ uint32_t field_group(uint32_t w)
-{
-    return (J / 4 == 0) ? w : (w >> (BITS * 4 * (J / 4)));
-}
-
 template <int BITS>
 __device__ __forceinline__ float code_f_rt(uint32_t w, int j)
 {

@@ -10,18 +10,19 @@ namespace adkv {
 // (half2 per lane) and per supergroup it writes 256 contiguous bytes (uint2 per lane).  The next
 // word's tokens are fetched while the current word is quantised.
 constexpr int kEncThreads = kD / 2;
+constexpr int kEncStages = 4;   // 32-token (8 KB) tiles of fp16 input in flight per CTA
 
 // Eight tokens (fields J0 .. J0+7 of the word being assembled) for the two channels of a thread,
 // speculative quantiser; returns true when some code is in doubt and the group must be redone.
 template <int BITS, bool GUARDED, int J0>
-__device__ __forceinline__ bool encode_group(const __half2 (&xin)[8], Chan (&ch)[2], uint32_t (&word)[2],
-                                             float smin, float smax)
+__device__ __forceinline__ bool encode_group(const __half2 *xin /* 8 rows of kD/2 */, Chan (&ch)[2],
+                                             uint32_t (&word)[2], float smin, float smax)
 {
     using C = Codec<BITS>;
     bool doubt = !(ch[0].s < 1e29f) || !(ch[1].s < 1e29f);   // reciprocal would flush to zero
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
-        const float2 x = __half22float2(xin[j]);
+        const float2 x = __half22float2(xin[j * (kD / 2)]);
         const float xs[2] = {x.x, x.y};
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -65,6 +66,14 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(uint32_t *__restric
     SafeRange safe;
     safe.template init<BITS, 2>(beta, target, smin, smax);
 
+    __shared__ alignas(128) __half buf[kEncStages][32 * kD];
+    __shared__ uint64_t bar[kEncStages];
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kEncStages; ++i) mbar_init(&bar[i], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
     uint2 *w = reinterpret_cast<uint2 *>(cache + size_t(bh) * n_super_cap * kD + c0);       // stride kD/2 per word row
     const __half2 *xs = reinterpret_cast<const __half2 *>(x + size_t(bh) * T * kD + c0);    // stride kD/2 per token
     constexpr int RS = kD / 2;
@@ -100,43 +109,57 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(uint32_t *__restric
             word[0] = word[1] = 0u;
         }
     }
-    // groups of 8 tokens, loads of the next group in flight while the current one is quantised
+    // Groups of 8 tokens.  The fp16 rows of the stream are contiguous, so they are staged through a
+    // ring of 32-token tiles filled by bulk copies (1-D TMA, issued by thread 0) that run ahead of
+    // the quantiser by kEncStages - 1 tiles.
     const int n_groups = (t_end - t) / 8;
-    __half2 cur[8], nxt[8];
-    if (n_groups > 0) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) cur[j] = xs[size_t(t - t_start + j) * RS];
-    }
+    const int n_tiles = (n_groups + 3) / 4;
+    const __half *src = x + (size_t(bh) * T + (t - t_start)) * kD;
+    auto issue = [&](int i) {
+        const uint32_t bytes = uint32_t(min(4, n_groups - 4 * i)) * 8 * kD * 2;
+        mbar_expect_tx(&bar[i % kEncStages], bytes);
+        bulk_load(&buf[i % kEncStages][0], src + size_t(i) * 32 * kD, bytes, &bar[i % kEncStages]);
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < min(kEncStages, n_tiles); ++i) issue(i);
 #pragma unroll 1
-    for (int g = 0; g < n_groups; ++g, t += 8) {
-        if (g + 1 < n_groups) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) nxt[j] = xs[size_t(t - t_start + 8 + j) * RS];
+    for (int i = 0; i < n_tiles; ++i) {
+        const bool landed = mbar_wait_bounded(&bar[i % kEncStages], (i / kEncStages) & 1, kStatKWait);
+        if (!__syncthreads_and(landed)) {
+            // give up as one CTA; let copies already in flight land (bounded) before the memory is released
+            for (int k = i; k < min(n_tiles, i + kEncStages); ++k)
+                if (!mbar_wait_bounded(&bar[k % kEncStages], (k / kEncStages) & 1, kStatDrain)) break;
+            return;
         }
-        const Chan saved[2] = {ch[0], ch[1]};
-        const uint32_t word_in[2] = {word[0], word[1]};
-        const bool second = C::TPW == 16 && (t & 8);
-        bool doubt;
-        if (safe.holds(ch)) {
-            doubt = second ? encode_group<BITS, false, 8 % C::TPW>(cur, ch, word, smin, smax)
-                           : encode_group<BITS, false, 0>(cur, ch, word, smin, smax);
-        } else {
-            doubt = second ? encode_group<BITS, true, 8 % C::TPW>(cur, ch, word, smin, smax)
-                           : encode_group<BITS, true, 0>(cur, ch, word, smin, smax);
+        const int ng = min(4, n_groups - 4 * i);
+#pragma unroll 1
+        for (int g = 0; g < ng; ++g, t += 8) {
+            const __half2 *rows = reinterpret_cast<const __half2 *>(&buf[i % kEncStages][0]) + g * 8 * RS + threadIdx.x;
+            const Chan saved[2] = {ch[0], ch[1]};
+            const uint32_t word_in[2] = {word[0], word[1]};
+            const bool second = C::TPW == 16 && (t & 8);
+            bool doubt;
+            if (safe.holds(ch)) {
+                doubt = second ? encode_group<BITS, false, 8 % C::TPW>(rows, ch, word, smin, smax)
+                               : encode_group<BITS, false, 0>(rows, ch, word, smin, smax);
+            } else {
+                doubt = second ? encode_group<BITS, true, 8 % C::TPW>(rows, ch, word, smin, smax)
+                               : encode_group<BITS, true, 0>(rows, ch, word, smin, smax);
+            }
+            if (doubt) {   // rare, per thread: redo the group from the saved state with the exact quantiser
+                ch[0] = saved[0];
+                ch[1] = saved[1];
+                word[0] = word_in[0];
+                word[1] = word_in[1];
+                for (int j = 0; j < 8; ++j) exact_token(t + j, word);
+            }
+            if ((t + 8) % C::TPW == 0) {
+                w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
+                word[0] = word[1] = 0u;
+            }
         }
-        if (doubt) {   // rare, per thread: redo the group from the saved state with the exact quantiser
-            ch[0] = saved[0];
-            ch[1] = saved[1];
-            word[0] = word_in[0];
-            word[1] = word_in[1];
-            for (int j = 0; j < 8; ++j) exact_token(t + j, word);
-        }
-        if ((t + 8) % C::TPW == 0) {
-            w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
-            word[0] = word[1] = 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+        __syncthreads();   // every thread is done with this stage
+        if (threadIdx.x == 0 && i + kEncStages < n_tiles) issue(i + kEncStages);
     }
     // trailing tokens; unused fields of the last word stay zero
     for (; t < t_end; ++t) exact_token(t, word);
@@ -176,6 +199,16 @@ __global__ void __launch_bounds__(kD) append_kernel(uint32_t *__restrict__ cache
 
 using namespace adkv;
 
+// Status word of this translation unit (read and cleared by adkv_device_status).
+ADKV_HIDDEN int adkv_tu_status_encode(int *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
+    if (e != cudaSuccess) return int(e);
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return e == cudaSuccess ? 0 : int(e);
+}
+
 extern "C" {
 
 int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, int B, int H, int T, int D,
@@ -185,7 +218,7 @@ int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, in
     if (t_start < 0) return ADKV_E_SHAPE;
     if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
     if (t_start > 0 && !tail) return ADKV_E_START;
-    if ((reinterpret_cast<uintptr_t>(cache) & 7u) || (reinterpret_cast<uintptr_t>(x) & 3u) ||
+    if ((reinterpret_cast<uintptr_t>(cache) & 7u) || (reinterpret_cast<uintptr_t>(x) & 15u) ||
         (reinterpret_cast<uintptr_t>(tail) & 7u) || (reinterpret_cast<uintptr_t>(p->zp_init) & 3u) ||
         (reinterpret_cast<uintptr_t>(p->scale_init) & 3u) || (reinterpret_cast<uintptr_t>(p->alpha) & 3u) ||
         (reinterpret_cast<uintptr_t>(p->beta) & 3u) || (reinterpret_cast<uintptr_t>(p->target) & 3u))
