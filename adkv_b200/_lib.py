@@ -21,6 +21,10 @@ SIGNATURES = {
     "adkv_strerror": [c_int],
     "adkv_encode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                     c_float, c_float, c_void_p],
+    "adkv_encode_kv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "adkv_append_kv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "adkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                     c_float, c_float, c_void_p],
     "adkv_forward_qk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

@@ -104,10 +104,11 @@ class KVCacheLayer:
         key = key_states.to(torch.float16).contiguous()
         value = value_states.to(torch.float16).contiguous()
         v = lambda t: t.view(H, C)
-        gemv.encode_kv(self._key_buf, key, v(key_zp_init), v(key_scale_init), v(key_alpha), v(key_beta),
-                       v(key_quant_target), SCALE_MIN, SCALE_MAX, bits=self.bits)
-        gemv.encode_kv(self._value_buf, value, v(value_zp_init), v(value_scale_init), v(value_alpha),
-                       v(value_beta), v(value_quant_target), SCALE_MIN, SCALE_MAX, bits=self.bits)
+        gemv.encode_kv_pair(self._key_buf, key,
+                            (v(key_zp_init), v(key_scale_init), v(key_alpha), v(key_beta), v(key_quant_target)),
+                            self._value_buf, value,
+                            (v(value_zp_init), v(value_scale_init), v(value_alpha), v(value_beta),
+                             v(value_quant_target)), SCALE_MIN, SCALE_MAX, bits=self.bits)
         self._quant_len += T
 
     # ------------------------------------------------------------------ decode

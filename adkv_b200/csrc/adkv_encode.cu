@@ -36,13 +36,27 @@ __device__ __forceinline__ bool encode_group(const __half2 *xin /* 8 rows of kD/
     return doubt;
 }
 
+// One tensor (K or V) of a launch; blockIdx.y selects it, so K and V of a layer are quantised side by side.
+struct EncTensor {
+    uint32_t *cache;
+    const __half *x;
+    ParamPtrs p;
+    float *tail;
+};
+struct EncBatch {
+    EncTensor t[2];
+};
+
 template <int BITS>
-__global__ void __launch_bounds__(kEncThreads) encode_kernel(uint32_t *__restrict__ cache,
-                                                             const __half *__restrict__ x, ParamPtrs p,
-                                                             float *__restrict__ tail, int H, int T, int n_super_cap,
+__global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int H, int T, int n_super_cap,
                                                              int t_start, float smin, float smax)
 {
     using C = Codec<BITS>;
+    const EncTensor &et = batch.t[blockIdx.y];
+    uint32_t *__restrict__ cache = et.cache;
+    const __half *__restrict__ x = et.x;
+    const ParamPtrs p = et.p;
+    float *__restrict__ tail = et.tail;
     const int bh = blockIdx.x, h = bh % H, c0 = 2 * threadIdx.x;
     const size_t po = size_t(h) * kD + c0;
     Chan ch[2];
@@ -172,11 +186,15 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(uint32_t *__restric
 
 // Single-token append from the persisted tail state.
 template <int BITS>
-__global__ void __launch_bounds__(kD) append_kernel(uint32_t *__restrict__ cache, const __half *__restrict__ x_new,
-                                                    ParamPtrs p, float *__restrict__ tail, int H, int T,
-                                                    int n_super_cap, float smin, float smax)
+__global__ void __launch_bounds__(kD) append_kernel(EncBatch batch, int H, int T, int n_super_cap, float smin,
+                                                    float smax)
 {
     using C = Codec<BITS>;
+    const EncTensor &et = batch.t[blockIdx.y];
+    uint32_t *__restrict__ cache = et.cache;
+    const __half *__restrict__ x_new = et.x;
+    const ParamPtrs p = et.p;
+    float *__restrict__ tail = et.tail;
     const int bh = blockIdx.x, h = bh % H, c = threadIdx.x;
     const size_t po = size_t(h) * kD + c;
     Chan ch;
@@ -209,31 +227,71 @@ ADKV_HIDDEN int adkv_tu_status_encode(int *out)
     return e == cudaSuccess ? 0 : int(e);
 }
 
-extern "C" {
-
-int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, int B, int H, int T, int D,
-                int n_super_cap, int bits, int t_start, float scale_min, float scale_max, void *stream)
+static int encode_check(const void *cache, const void *x, const adkv_params *p, const void *tail, int T, int t_start)
 {
     if (!cache || (!x && T > 0) || !params_ok(p)) return ADKV_E_NULL;
-    if (t_start < 0) return ADKV_E_SHAPE;
-    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
     if (t_start > 0 && !tail) return ADKV_E_START;
     if ((reinterpret_cast<uintptr_t>(cache) & 7u) || (reinterpret_cast<uintptr_t>(x) & 15u) ||
         (reinterpret_cast<uintptr_t>(tail) & 7u) || (reinterpret_cast<uintptr_t>(p->zp_init) & 3u) ||
         (reinterpret_cast<uintptr_t>(p->scale_init) & 3u) || (reinterpret_cast<uintptr_t>(p->alpha) & 3u) ||
         (reinterpret_cast<uintptr_t>(p->beta) & 3u) || (reinterpret_cast<uintptr_t>(p->target) & 3u))
         return ADKV_E_ALIGN;
-    if (B * H == 0 || (T == 0 && !(tail && t_start == 0))) return 0;
+    return 0;
+}
+
+static EncTensor enc_tensor(void *cache, const void *x, const adkv_params *p, void *tail)
+{
+    return EncTensor{static_cast<uint32_t *>(cache), static_cast<const __half *>(x), to_ptrs(p),
+                     static_cast<float *>(tail)};
+}
+
+static int launch_encode(const EncBatch &b, int n, int B, int H, int T, int n_super_cap, int bits, int t_start,
+                         float smin, float smax, void *stream)
+{
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (bits == 4)
-        encode_kernel<4><<<B * H, kEncThreads, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x),
-                                              to_ptrs(p), static_cast<float *>(tail), H, T, n_super_cap, t_start,
-                                              scale_min, scale_max);
-    else
-        encode_kernel<2><<<B * H, kEncThreads, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x),
-                                              to_ptrs(p), static_cast<float *>(tail), H, T, n_super_cap, t_start,
-                                              scale_min, scale_max);
+    const dim3 grid(B * H, n);
+    if (bits == 4) encode_kernel<4><<<grid, kEncThreads, 0, s>>>(b, H, T, n_super_cap, t_start, smin, smax);
+    else encode_kernel<2><<<grid, kEncThreads, 0, s>>>(b, H, T, n_super_cap, t_start, smin, smax);
     return launch_status();
+}
+
+static int launch_append(const EncBatch &b, int n, int B, int H, int T, int n_super_cap, int bits, float smin,
+                         float smax, void *stream)
+{
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid(B * H, n);
+    if (bits == 4) append_kernel<4><<<grid, kD, 0, s>>>(b, H, T, n_super_cap, smin, smax);
+    else append_kernel<2><<<grid, kD, 0, s>>>(b, H, T, n_super_cap, smin, smax);
+    return launch_status();
+}
+
+extern "C" {
+
+int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, int B, int H, int T, int D,
+                int n_super_cap, int bits, int t_start, float scale_min, float scale_max, void *stream)
+{
+    if (t_start < 0) return ADKV_E_SHAPE;
+    if (int rc = encode_check(cache, x, p, tail, T, t_start)) return rc;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
+    if (B * H == 0 || (T == 0 && !(tail && t_start == 0))) return 0;
+    EncBatch b{};
+    b.t[0] = enc_tensor(cache, x, p, tail);
+    return launch_encode(b, 1, B, H, T, n_super_cap, bits, t_start, scale_min, scale_max, stream);
+}
+
+int adkv_encode_kv(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *v_cache, const void *v,
+                   const adkv_params *vp, void *v_tail, int B, int H, int T, int D, int n_super_cap, int bits,
+                   int t_start, float scale_min, float scale_max, void *stream)
+{
+    if (t_start < 0) return ADKV_E_SHAPE;
+    if (int rc = encode_check(k_cache, k, kp, k_tail, T, t_start)) return rc;
+    if (int rc = encode_check(v_cache, v, vp, v_tail, T, t_start)) return rc;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
+    if (B * H == 0 || (T == 0 && !((k_tail || v_tail) && t_start == 0))) return 0;
+    EncBatch b{};
+    b.t[0] = enc_tensor(k_cache, k, kp, k_tail);
+    b.t[1] = enc_tensor(v_cache, v, vp, v_tail);
+    return launch_encode(b, 2, B, H, T, n_super_cap, bits, t_start, scale_min, scale_max, stream);
 }
 
 int adkv_append(void *cache, const void *x_new, const adkv_params *p, void *tail, int B, int H, int T, int D,
@@ -242,16 +300,23 @@ int adkv_append(void *cache, const void *x_new, const adkv_params *p, void *tail
     if (!cache || !x_new || !tail || !params_ok(p)) return ADKV_E_NULL;
     if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, T + 1)) return rc;
     if (B * H == 0) return 0;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (bits == 4)
-        append_kernel<4><<<B * H, kD, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x_new),
-                                              to_ptrs(p), static_cast<float *>(tail), H, T, n_super_cap, scale_min,
-                                              scale_max);
-    else
-        append_kernel<2><<<B * H, kD, 0, s>>>(static_cast<uint32_t *>(cache), static_cast<const __half *>(x_new),
-                                              to_ptrs(p), static_cast<float *>(tail), H, T, n_super_cap, scale_min,
-                                              scale_max);
-    return launch_status();
+    EncBatch b{};
+    b.t[0] = enc_tensor(cache, x_new, p, tail);
+    return launch_append(b, 1, B, H, T, n_super_cap, bits, scale_min, scale_max, stream);
+}
+
+int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *v_cache,
+                   const void *v_new, const adkv_params *vp, void *v_tail, int B, int H, int T, int D,
+                   int n_super_cap, int bits, float scale_min, float scale_max, void *stream)
+{
+    if (!k_cache || !k_new || !k_tail || !params_ok(kp) || !v_cache || !v_new || !v_tail || !params_ok(vp))
+        return ADKV_E_NULL;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (B * H == 0) return 0;
+    EncBatch b{};
+    b.t[0] = enc_tensor(k_cache, k_new, kp, k_tail);
+    b.t[1] = enc_tensor(v_cache, v_new, vp, v_tail);
+    return launch_append(b, 2, B, H, T, n_super_cap, bits, scale_min, scale_max, stream);
 }
 
 }  // extern "C"

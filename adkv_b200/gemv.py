@@ -24,7 +24,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["encode_kv", "forward_qk", "forward_ov", "decode_attn", "append_kv", "n_super_for"]
+__all__ = ["encode_kv", "forward_qk", "forward_ov", "decode_attn", "append_kv", "encode_kv_pair",
+           "append_kv_pair", "n_super_for"]
 
 
 def n_super_for(tokens: int, bits: int = 4) -> int:
@@ -88,6 +89,68 @@ def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min
                                      t_start, scale_min, scale_max, _stream(kv_cache))
     _lib.check(rc, "encode_kv")
     return kv_cache
+
+
+def _tail_ptr(tail, B, H, D):
+    if tail is None:
+        return None
+    _require(tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape == (B, H, 2, D),
+             "tail must be contiguous float32 [B, nh, 2, DIM]")
+    return tail.data_ptr()
+
+
+def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min, scale_max, *, bits: int = 4,
+                   k_tail=None, v_tail=None, t_start: int = 0):
+    """``encode_kv`` for the K and V tensors of one layer in a single launch (same contract each;
+    replaces the two calls of ``src/adkv/hf/llama_adkv.py:144-153``)."""
+    _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "kv_new must be float16")
+    B, H, n_super_cap, D = _cache_dims(k_cache, "kv_cache")
+    _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
+             "v_cache must match k_cache")
+    _require(k_cache.is_contiguous() and v_cache.is_contiguous(), "kv_cache must be contiguous (written in place)")
+    _require(k_new.dim() == 4 and k_new.shape == v_new.shape, "k_new / v_new must both be [B, nh, T, DIM]")
+    _require(k_new.shape[0] == B and k_new.shape[1] == H and k_new.shape[3] == D,
+             "kv_cache channel groups do not match kv_new head dim")
+    T = k_new.shape[2]
+    need = n_super_for(t_start + T, bits)
+    _require(need <= n_super_cap,
+             f"kv_cache capacity too small: need {need} supergroups for {t_start + T} tokens, have {n_super_cap}")
+    names = ("kv_zp", "kv_sc", "kv_alpha", "kv_beta", "kv_t")
+    kp, keep_k = _params(names, tuple(k_params), H, D, k_cache.device)
+    vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
+    xk, xv = k_new.contiguous(), v_new.contiguous()
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().adkv_encode_kv(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                        _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
+                                        ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D, n_super_cap,
+                                        bits, t_start, scale_min, scale_max, _stream(k_cache))
+    _lib.check(rc, "encode_kv_pair")
+    return k_cache, v_cache
+
+
+def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v_tail, T: int, scale_min, scale_max,
+                   *, bits: int = 4):
+    """``append_kv`` for K and V of one layer in a single launch."""
+    B, H, n_super_cap, D = _cache_dims(k_cache, "cache")
+    _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
+             "v_cache must match k_cache")
+    _require(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache must be contiguous (appended in place)")
+    _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "x_new must be float16")
+    _require(k_new.numel() == B * H * D and v_new.numel() == B * H * D, "x_new must be [B, nh, 1, DIM]")
+    _require(T >= 0, "T must be non-negative")
+    _require(T // (32 // bits) < n_super_cap, f"cache has no free supergroup to append token {T}")
+    _require(k_tail is not None and v_tail is not None, "append needs both tail states")
+    names = ("zp", "sc", "alpha", "beta", "target")
+    kp, keep_k = _params(names, tuple(k_params), H, D, k_cache.device)
+    vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
+    xk, xv = k_new.contiguous(), v_new.contiguous()
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().adkv_append_kv(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                        _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
+                                        ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D, n_super_cap,
+                                        bits, scale_min, scale_max, _stream(k_cache))
+    _lib.check(rc, "append_kv_pair")
+    return k_cache, v_cache
 
 
 def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min, scale_max, *, bits: int = 4):

@@ -71,6 +71,14 @@ int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail,
                 int B, int H, int T, int D, int n_super_cap, int bits, int t_start,
                 float scale_min, float scale_max, void *stream);
 
+/* The same for K and V of one layer in ONE launch (twice the streams in flight: the quantiser is bound by
+ * its token-sequential chain, not by bandwidth).  Replaces the pair of encode_kv calls of
+ * src/adkv/hf/llama_adkv.py:144-153.  Both tensors share shapes, bits, t_start and clamp bounds. */
+int adkv_encode_kv(void *k_cache, const void *k, const adkv_params *kp, void *k_tail,
+                   void *v_cache, const void *v, const adkv_params *vp, void *v_tail,
+                   int B, int H, int T, int D, int n_super_cap, int bits, int t_start,
+                   float scale_min, float scale_max, void *stream);
+
 /* Single-token append from a persisted tail state (no replay).  No direct counterpart in the
  * reference, whose append happens inside forward_qk/forward_ov after a full replay
  * (src/adkv/kernel/gemv.cu:91-146, 744-764); same arithmetic, same slot.
@@ -78,6 +86,12 @@ int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail,
 int adkv_append(void *cache, const void *x_new, const adkv_params *p, void *tail,
                 int B, int H, int T, int D, int n_super_cap, int bits,
                 float scale_min, float scale_max, void *stream);
+
+/* adkv_append for K and V of one layer in one launch. */
+int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail,
+                   void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail,
+                   int B, int H, int T, int D, int n_super_cap, int bits,
+                   float scale_min, float scale_max, void *stream);
 
 /* q.K^T over the packed cache + append of k_new as token T + self logit.  Replaces forward_qk
  * (src/adkv/kernel/gemv.cu:883-939, called from src/adkv/hf/llama_adkv.py:264).

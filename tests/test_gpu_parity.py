@@ -83,6 +83,26 @@ def test_chunked_encode_and_append_equal_one_shot(bits):
     assert torch.equal(tail_full.view(torch.int32), tail.view(torch.int32))
 
 
+@pytest.mark.parametrize("bits", [4, 2])
+def test_pair_launches_equal_single_tensor_launches(bits):
+    B, H, D, T = 2, 3, 128, 45
+    k, v = synth.gen_kv(31, B, H, T + 3, D), synth.gen_kv(32, B, H, T + 3, D)
+    kp, vp = dev(synth.gen_params(33, H, D, bits)), dev(synth.gen_params(34, H, D, bits))
+    ns = orc.n_super_for(T + 3, bits)
+    mk = lambda: torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    mt = lambda: torch.empty(B, H, 2, D, dtype=torch.float32, device="cuda")
+    k1, v1, k2, v2, tk1, tv1, tk2, tv2 = mk(), mk(), mk(), mk(), mt(), mt(), mt(), mt()
+    gemv.encode_kv(k1, dev(k[:, :, :T]), *kp, SMIN, SMAX, bits=bits, tail=tk1)
+    gemv.encode_kv(v1, dev(v[:, :, :T]), *vp, SMIN, SMAX, bits=bits, tail=tv1)
+    gemv.encode_kv_pair(k2, dev(k[:, :, :T]), kp, v2, dev(v[:, :, :T]), vp, SMIN, SMAX, bits=bits, k_tail=tk2, v_tail=tv2)
+    for t in range(T, T + 3):
+        gemv.append_kv(k1, dev(k[:, :, t:t + 1]), *kp, tk1, t, SMIN, SMAX, bits=bits)
+        gemv.append_kv(v1, dev(v[:, :, t:t + 1]), *vp, tv1, t, SMIN, SMAX, bits=bits)
+        gemv.append_kv_pair(k2, dev(k[:, :, t:t + 1]), kp, tk2, v2, dev(v[:, :, t:t + 1]), vp, tv2, t, SMIN, SMAX, bits=bits)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(tk1.view(torch.int32), tk2.view(torch.int32)) and torch.equal(tv1.view(torch.int32), tv2.view(torch.int32))
+
+
 # ------------------------------------------------------------------------------- decode
 
 CASES = [

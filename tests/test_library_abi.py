@@ -52,7 +52,7 @@ def test_cpu_tensors_are_refused():
 
 def test_null_and_shape_errors_from_the_c_abi():
     lib = _lib.load()
-    P = _lib.Params(1, 1, 1, 1, 1)
+    P = _lib.Params(16, 16, 16, 16, 16)
     import ctypes
     pp = ctypes.addressof(P)
     assert lib.adkv_encode(None, 16, pp, None, 1, 1, 8, 128, 1, 4, 0, 0.1, 1.0, None) == -1
