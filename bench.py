@@ -200,7 +200,7 @@ def pick_sample_streams(w, target_s: float) -> int:
     """Streams whose decode takes about `target_s` seconds of host time, from a 1-stream-per-thread probe."""
     from oracle import c_oracle
     c_oracle.build()
-    thr = c_oracle.num_threads()
+    thr = c_oracle.use_all_cores()
     probe = cpu_sample(w, thr)
     cpu_step(w, probe)
     t0 = time.perf_counter()
@@ -271,6 +271,7 @@ def check_against_oracle(w, st, out, n_streams, torch):
 
     from adkv_b200 import synth
     from oracle import c_oracle
+    c_oracle.use_all_cores()
     Hq, Hkv, D, T, bits = w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
     G = Hq // Hkv
     nb = max(1, min(w["B"], (n_streams + Hkv - 1) // Hkv))
@@ -371,7 +372,8 @@ def run_encode(args, w, name):
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # CPU restatement on a bounded sample of sequences; also checks the GPU's codes for them
-    nb = 1
+    c_oracle.use_all_cores()
+    nb = min(B, 4)
     kc_cpu = np.zeros((nb, H, ns, D // 4, 4, 4), np.uint8)
     xk = hk[:nb].numpy()
     f = lambda ps: tuple(p.float().cpu().numpy() for p in ps)

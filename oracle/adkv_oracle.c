@@ -64,6 +64,16 @@ static inline void advance1(float q, float rh, float *zp, float *s, float alpha,
     *s = clampf(*s + *s * beta * err, smin, smax);
 }
 
+/* torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the timed baseline sets the count itself. */
+void oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void)
 {
 #ifdef _OPENMP

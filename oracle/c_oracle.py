@@ -47,6 +47,13 @@ def num_threads() -> int:
     return lib().oracle_num_threads()
 
 
+def use_all_cores() -> int:
+    """Let OpenMP use every core this process may run on (launchers often export OMP_NUM_THREADS=1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(n)
+    return num_threads()
+
+
 def encode(cache: np.ndarray, x16: np.ndarray, params, bits, smin, smax, want_tail=False):
     """cache uint8 [B,H,ns,D/4,4,4] (in place), x16 float16 [B,H,T,D]."""
     B, H, T, D = x16.shape
