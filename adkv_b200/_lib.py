@@ -25,6 +25,12 @@ SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "adkv_append_kv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "adkv_encode_kv_ckpt": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_void_p],
+    "adkv_append_kv_ckpt": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_void_p],
+    "adkv_decode_attn_ckpt_scratch_bytes": [c_int, c_int, c_int, c_int, c_int],
+    "adkv_decode_attn_ckpt": [c_void_p] * 9 + [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_uint,
+                              c_void_p],
     "adkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                     c_float, c_float, c_void_p],
     "adkv_forward_qk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -36,7 +42,7 @@ SIGNATURES = {
                          c_float, c_float, c_float, c_uint, c_void_p],
     "adkv_device_status": [c_void_p, c_void_p],
 }
-_RESTYPE = {"adkv_strerror": ctypes.c_char_p}
+_RESTYPE = {"adkv_strerror": ctypes.c_char_p, "adkv_decode_attn_ckpt_scratch_bytes": c_longlong}
 
 
 class Params(ctypes.Structure):

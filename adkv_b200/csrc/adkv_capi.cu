@@ -5,6 +5,7 @@
 ADKV_HIDDEN int adkv_tu_status_fused(int *out);
 ADKV_HIDDEN int adkv_tu_status_unfused(int *out);
 ADKV_HIDDEN int adkv_tu_status_encode(int *out);
+ADKV_HIDDEN int adkv_tu_status_split(int *out);
 
 extern "C" {
 
@@ -21,6 +22,7 @@ const char *adkv_strerror(int code)
     case ADKV_E_CAPACITY: return "adkv: cache capacity too small for the tokens to be written";
     case ADKV_E_ALIGN: return "adkv: pointer not sufficiently aligned (cache 16 bytes, fp16 rows 8 bytes)";
     case ADKV_E_START: return "adkv: t_start > 0 needs a tail state";
+    case ADKV_E_SCRATCH: return "adkv: scratch memory too small for this problem";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "adkv: unknown error";
     }
 }
@@ -30,11 +32,12 @@ int adkv_device_status(int *status, void *stream)
     if (!status) return ADKV_E_NULL;
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return int(e);
-    int a = 0, b = 0, c = 0;
+    int a = 0, b = 0, c = 0, d = 0;
     if (int rc = adkv_tu_status_fused(&a)) return rc;
     if (int rc = adkv_tu_status_unfused(&b)) return rc;
     if (int rc = adkv_tu_status_encode(&c)) return rc;
-    *status = a ? a : (b ? b : c);
+    if (int rc = adkv_tu_status_split(&d)) return rc;
+    *status = a ? a : (b ? b : (c ? c : d));
     return 0;
 }
 

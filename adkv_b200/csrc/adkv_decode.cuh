@@ -134,6 +134,32 @@ __device__ __forceinline__ void reduce8(float (&part)[G][8], float *red, int lan
     }
 }
 
+// The part of a stream one warp pair works on.  The whole-stream kernels use {0, T, true, nullptr, nullptr};
+// the checkpointed kernel gives every segment its own pair of warps.
+struct Seg {
+    int t_begin;          // first token replayed (a multiple of kTileTok)
+    int t_end;            // one past the last token replayed
+    bool append;          // quantise x_new as token t_end (== T), write it, add its own term
+    const float *init;    // state before token t_begin of this stream, [2][kD] (zp, scale); nullptr = parameters
+    float *ckpt_out;      // where to store the state after the appended token, [2][kD]; nullptr = nowhere
+};
+
+__device__ __forceinline__ void load_init_state(Chan (&ch)[4], const float *init, int lane)
+{
+    if (init) {
+        const float4 zp = *reinterpret_cast<const float4 *>(init + 4 * lane);
+        const float4 sc = *reinterpret_cast<const float4 *>(init + kD + 4 * lane);
+        ch[0].zp = zp.x; ch[1].zp = zp.y; ch[2].zp = zp.z; ch[3].zp = zp.w;
+        ch[0].s = sc.x; ch[1].s = sc.y; ch[2].s = sc.z; ch[3].s = sc.w;
+    }
+}
+
+__device__ __forceinline__ void store_state(float *dst, const Chan (&ch)[4], int lane)
+{
+    *reinterpret_cast<float4 *>(dst + 4 * lane) = make_float4(ch[0].zp, ch[1].zp, ch[2].zp, ch[3].zp);
+    *reinterpret_cast<float4 *>(dst + kD + 4 * lane) = make_float4(ch[0].s, ch[1].s, ch[2].s, ch[3].s);
+}
+
 struct KArgs {
     const __half *q;        // [B, Hq, D]
     uint8_t *cache;         // [B, Hkv, n_super_cap, D] words
@@ -150,7 +176,7 @@ struct KArgs {
 //   void put_self(int g, float v)     lane 0
 //   void finish(int lane)
 template <int BITS, int G, bool EXACT, class Sink>
-__device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, uint8_t *ring_buf,
+__device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, float *red, Sink &sink)
 {
     using C = Codec<BITS>;
@@ -160,12 +186,15 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
     FieldConsts<BITS> fc;
     fc.init();
     load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
+    load_init_state(ch, seg.init, lane);
     float qv[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane);
 
     uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
-    StreamRing<BITS> ring{ring_buf, ring_bar, stream, (a.T + kTileTok - 1) / kTileTok, a.T, kStatKWait};
+    const int n_tok = seg.t_end - seg.t_begin;
+    StreamRing<BITS> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * kD * 4,
+                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait};
     ring.prologue(lane);
 
     bool ok = true;
@@ -174,7 +203,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
         if (!(ok = ring.wait(i))) break;
         if (!(ok = sink.begin_tile(i))) break;
         const uint4 *tile = ring.tile(i, lane);
-        const int ntok = min(kTileTok, a.T - i * kTileTok);
+        const int ntok = min(kTileTok, n_tok - i * kTileTok);
         float part[G][8], sum[G];
         if (ntok == kTileTok) {
             // not unrolled over the words of the tile: the loop body must stay resident in the
@@ -217,6 +246,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
         return;
     }
 
+    if (!seg.append) return;
     // Append k_new as token T with the state left by token T-1, then its own logit from the
     // dequantised value.
     float xn[4], xh[4];
@@ -231,8 +261,10 @@ __device__ __forceinline__ void k_warp(const KArgs &a, int b, int h, int lane, u
         const float q = quantize<BITS>(xn[c], ch[c], rh);
         xh[c] = __fadd_rn(rh, ch[c].zp);
         ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+        if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
     }
     *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+    if (seg.ckpt_out) store_state(seg.ckpt_out, ch, lane);
     if (!sink.begin_tile(ring.n_tiles)) return;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -295,9 +327,9 @@ struct VArgs {
 //        fill wts[g][0..31] for tile i (0 for tokens >= ntok); may rescale acc (online softmax);
 //        false = bounded wait gave up
 //   bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
-//   float norm(int g)        final divisor (1 for pre-normalised weights)
+//   void store(const VArgs&, int b, int h, int lane, const float (&acc)[G][4])   write the result
 template <int BITS, int G, bool EXACT, class Src>
-__device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, uint8_t *ring_buf,
+__device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, const float *wts, Src &src)
 {
     using C = Codec<BITS>;
@@ -307,6 +339,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
     FieldConsts<BITS> fc;
     fc.init();
     load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
+    load_init_state(ch, seg.init, lane);
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -314,13 +347,15 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
         for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
 
     uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
-    StreamRing<BITS> ring{ring_buf, ring_bar, stream, (a.T + kTileTok - 1) / kTileTok, a.T, kStatVWait};
+    const int n_tok = seg.t_end - seg.t_begin;
+    StreamRing<BITS> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * kD * 4,
+                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait};
     ring.prologue(lane);
 
     bool ok = true;
     int i = 0;
     for (; i < ring.n_tiles; ++i) {
-        const int ntok = min(kTileTok, a.T - i * kTileTok);
+        const int ntok = min(kTileTok, n_tok - i * kTileTok);
         if (!(ok = src.tile_weights(i, ntok, lane, acc))) break;
         if (!(ok = ring.wait(i))) break;
         const uint4 *tile = ring.tile(i, lane);
@@ -358,29 +393,44 @@ __device__ __forceinline__ void v_warp(const VArgs &a, int b, int h, int lane, u
         return;
     }
 
-    float w_self[G];
-    if (!src.self_weight(lane, acc, w_self, a.T)) return;
-
-    float xn[4], xh[4];
-    load_half4(xn, a.x_new + size_t(bh) * kD + 4 * lane);
-    uint4 *slot = reinterpret_cast<uint4 *>(stream) + size_t(a.T / C::TPW) * (kD / 4) + lane;
-    uint4 wv = *slot;
-    uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-    const int sh = BITS * (a.T % C::TPW);
+    if (seg.append) {
+        float w_self[G];
+        if (!src.self_weight(lane, acc, w_self, a.T)) return;
+        float xn[4], xh[4];
+        load_half4(xn, a.x_new + size_t(bh) * kD + 4 * lane);
+        uint4 *slot = reinterpret_cast<uint4 *>(stream) + size_t(a.T / C::TPW) * (kD / 4) + lane;
+        uint4 wv = *slot;
+        uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        const int sh = BITS * (a.T % C::TPW);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        float rh;
-        const float q = quantize<BITS>(xn[c], ch[c], rh);
-        xh[c] = __fadd_rn(rh, ch[c].zp);
-        ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+        for (int c = 0; c < 4; ++c) {
+            float rh;
+            const float q = quantize<BITS>(xn[c], ch[c], rh);
+            xh[c] = __fadd_rn(rh, ch[c].zp);
+            ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+            if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
+        }
+        *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+        if (seg.ckpt_out) store_state(seg.ckpt_out, ch, lane);
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[g][c] = fmaf(w_self[g], xh[c], acc[g][c]);
     }
-    *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+    src.store(a, b, h, lane, acc);
+}
+
+// Final division by the softmax denominator and fp16 store of the 4 channels of every head.
+template <int G, class Src>
+__device__ __forceinline__ void store_normalised(const Src &src, const VArgs &a, int b, int h, int lane,
+                                                 const float (&acc)[G][4])
+{
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         const float inv = 1.0f / src.norm(g);
         float o[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) o[c] = fmaf(w_self[g], xh[c], acc[g][c]) * inv;
+        for (int c = 0; c < 4; ++c) o[c] = acc[g][c] * inv;
         store_half4(a.out + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane, o);
     }
 }

@@ -164,6 +164,21 @@ __device__ __forceinline__ float quantize(float x, const Chan &c, float &rh)
     return q;
 }
 
+// State update after an appended token, in the arithmetic the replay uses (always with guard and clamp).
+template <bool EXACT>
+__device__ __forceinline__ void advance_like_replay(float q, float rh, Chan &c, float smin, float smax)
+{
+    float s_new;
+    if (EXACT) {
+        c.zp = __fadd_rn(c.zp, __fmul_rn(c.alpha, rh));
+        s_new = __fadd_rn(c.s, __fmul_rn(__fmul_rn(c.s, c.beta), __fsub_rn(fabsf(q), c.tc)));
+    } else {
+        c.zp = fmaf(c.alpha, rh, c.zp);
+        s_new = c.s * fmaf(c.beta, fabsf(q), c.tc);
+    }
+    c.s = fminf(fmaxf(s_new, smin), smax);
+}
+
 // Speculative form of quantize(): the quotient is formed with the approximate reciprocal (error
 // below 2.2e-6 for |v| < 16) and rounded with the 1.5*2^23 trick after clamping (clamp and
 // round-to-nearest-even commute because the limits are integers).  The result equals the canonical

@@ -42,14 +42,19 @@ struct EncTensor {
     const __half *x;
     ParamPtrs p;
     float *tail;
+    float *ckpt;   // state checkpoints [B*H][n_ckpt_cap][2][kD] or nullptr; entry k = state before token (k+1)*interval
+};
+struct CkptSpec {
+    int interval;     // tokens between checkpoints (multiple of 32), 0 = none
+    int n_ckpt_cap;
 };
 struct EncBatch {
     EncTensor t[2];
 };
 
 template <int BITS>
-__global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int H, int T, int n_super_cap,
-                                                             int t_start, float smin, float smax)
+__global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, CkptSpec cs, int H, int T,
+                                                             int n_super_cap, int t_start, float smin, float smax)
 {
     using C = Codec<BITS>;
     const EncTensor &et = batch.t[blockIdx.y];
@@ -105,6 +110,20 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int
         }
     };
 
+    // checkpoint k is written when the state before token (k+1)*interval is reached
+    float *ckpt = (et.ckpt && cs.interval > 0) ? et.ckpt + size_t(bh) * cs.n_ckpt_cap * 2 * kD + c0 : nullptr;
+    int next_ckpt = ckpt ? (t_start / cs.interval + 1) * cs.interval : 0x7fffffff;
+    auto checkpoint = [&](int t_reached) {
+        if (t_reached == next_ckpt) {
+            const int k = next_ckpt / cs.interval - 1;
+            if (k < cs.n_ckpt_cap) {
+                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * kD) = make_float2(ch[0].zp, ch[1].zp);
+                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * kD + kD) = make_float2(ch[0].s, ch[1].s);
+            }
+            next_ckpt += cs.interval;
+        }
+    };
+
     const int t_end = t_start + T;
     int t = t_start;
     uint32_t word[2] = {0u, 0u};
@@ -118,6 +137,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int
     // tokens up to the next multiple of 8
     for (; t < t_end && t % 8 != 0; ++t) {
         exact_token(t, word);
+        checkpoint(t + 1);
         if ((t + 1) % C::TPW == 0) {
             w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
             word[0] = word[1] = 0u;
@@ -167,6 +187,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int
                 word[1] = word_in[1];
                 for (int j = 0; j < 8; ++j) exact_token(t + j, word);
             }
+            checkpoint(t + 8);
             if ((t + 8) % C::TPW == 0) {
                 w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
                 word[0] = word[1] = 0u;
@@ -176,7 +197,10 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int
         if (threadIdx.x == 0 && i + kEncStages < n_tiles) issue(i + kEncStages);
     }
     // trailing tokens; unused fields of the last word stay zero
-    for (; t < t_end; ++t) exact_token(t, word);
+    for (; t < t_end; ++t) {
+        exact_token(t, word);
+        checkpoint(t + 1);
+    }
     if (t % C::TPW != 0) w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
     if (tail) {
         *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * kD + c0) = make_float2(ch[0].zp, ch[1].zp);
@@ -186,8 +210,8 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, int
 
 // Single-token append from the persisted tail state.
 template <int BITS>
-__global__ void __launch_bounds__(kD) append_kernel(EncBatch batch, int H, int T, int n_super_cap, float smin,
-                                                    float smax)
+__global__ void __launch_bounds__(kD) append_kernel(EncBatch batch, CkptSpec cs, int H, int T, int n_super_cap,
+                                                    float smin, float smax)
 {
     using C = Codec<BITS>;
     const EncTensor &et = batch.t[blockIdx.y];
@@ -211,6 +235,14 @@ __global__ void __launch_bounds__(kD) append_kernel(EncBatch batch, int H, int T
     advance_canonical(q, rh, ch, smin, smax);
     tail[size_t(bh) * 2 * kD + c] = ch.zp;
     tail[size_t(bh) * 2 * kD + kD + c] = ch.s;
+    if (et.ckpt && cs.interval > 0 && (T + 1) % cs.interval == 0) {
+        const int k = (T + 1) / cs.interval - 1;
+        if (k < cs.n_ckpt_cap) {
+            float *dst = et.ckpt + (size_t(bh) * cs.n_ckpt_cap + k) * 2 * kD;
+            dst[c] = ch.zp;
+            dst[kD + c] = ch.s;
+        }
+    }
 }
 
 }  // namespace adkv
@@ -239,29 +271,38 @@ static int encode_check(const void *cache, const void *x, const adkv_params *p, 
     return 0;
 }
 
-static EncTensor enc_tensor(void *cache, const void *x, const adkv_params *p, void *tail)
+static EncTensor enc_tensor(void *cache, const void *x, const adkv_params *p, void *tail, void *ckpt = nullptr)
 {
     return EncTensor{static_cast<uint32_t *>(cache), static_cast<const __half *>(x), to_ptrs(p),
-                     static_cast<float *>(tail)};
+                     static_cast<float *>(tail), static_cast<float *>(ckpt)};
+}
+
+static int ckpt_check(const void *k_ckpt, const void *v_ckpt, int interval, int n_ckpt_cap, int t_last_plus_1)
+{
+    if (interval <= 0 || interval % 32 != 0 || n_ckpt_cap < 0) return ADKV_E_SHAPE;
+    if (!k_ckpt || !v_ckpt) return ADKV_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(k_ckpt) & 15u) || (reinterpret_cast<uintptr_t>(v_ckpt) & 15u)) return ADKV_E_ALIGN;
+    if (t_last_plus_1 / interval > n_ckpt_cap) return ADKV_E_CAPACITY;
+    return 0;
 }
 
 static int launch_encode(const EncBatch &b, int n, int B, int H, int T, int n_super_cap, int bits, int t_start,
-                         float smin, float smax, void *stream)
+                         float smin, float smax, void *stream, CkptSpec cs = CkptSpec{0, 0})
 {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid(B * H, n);
-    if (bits == 4) encode_kernel<4><<<grid, kEncThreads, 0, s>>>(b, H, T, n_super_cap, t_start, smin, smax);
-    else encode_kernel<2><<<grid, kEncThreads, 0, s>>>(b, H, T, n_super_cap, t_start, smin, smax);
+    if (bits == 4) encode_kernel<4><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
+    else encode_kernel<2><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
     return launch_status();
 }
 
 static int launch_append(const EncBatch &b, int n, int B, int H, int T, int n_super_cap, int bits, float smin,
-                         float smax, void *stream)
+                         float smax, void *stream, CkptSpec cs = CkptSpec{0, 0})
 {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid(B * H, n);
-    if (bits == 4) append_kernel<4><<<grid, kD, 0, s>>>(b, H, T, n_super_cap, smin, smax);
-    else append_kernel<2><<<grid, kD, 0, s>>>(b, H, T, n_super_cap, smin, smax);
+    if (bits == 4) append_kernel<4><<<grid, kD, 0, s>>>(b, cs, H, T, n_super_cap, smin, smax);
+    else append_kernel<2><<<grid, kD, 0, s>>>(b, cs, H, T, n_super_cap, smin, smax);
     return launch_status();
 }
 
@@ -317,6 +358,41 @@ int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void
     b.t[0] = enc_tensor(k_cache, k_new, kp, k_tail);
     b.t[1] = enc_tensor(v_cache, v_new, vp, v_tail);
     return launch_append(b, 2, B, H, T, n_super_cap, bits, scale_min, scale_max, stream);
+}
+
+int adkv_encode_kv_ckpt(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                        void *v_cache, const void *v, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                        int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                        int t_start, float scale_min, float scale_max, void *stream)
+{
+    if (t_start < 0) return ADKV_E_SHAPE;
+    if (int rc = encode_check(k_cache, k, kp, k_tail, T, t_start)) return rc;
+    if (int rc = encode_check(v_cache, v, vp, v_tail, T, t_start)) return rc;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
+    if (int rc = ckpt_check(k_ckpt, v_ckpt, interval, n_ckpt_cap, t_start + T)) return rc;
+    if (B * H == 0 || (T == 0 && !((k_tail || v_tail) && t_start == 0))) return 0;
+    EncBatch b{};
+    b.t[0] = enc_tensor(k_cache, k, kp, k_tail, k_ckpt);
+    b.t[1] = enc_tensor(v_cache, v, vp, v_tail, v_ckpt);
+    return launch_encode(b, 2, B, H, T, n_super_cap, bits, t_start, scale_min, scale_max, stream,
+                         CkptSpec{interval, n_ckpt_cap});
+}
+
+int adkv_append_kv_ckpt(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                        void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                        int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                        float scale_min, float scale_max, void *stream)
+{
+    if (!k_cache || !k_new || !k_tail || !params_ok(kp) || !v_cache || !v_new || !v_tail || !params_ok(vp))
+        return ADKV_E_NULL;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (int rc = ckpt_check(k_ckpt, v_ckpt, interval, n_ckpt_cap, T + 1)) return rc;
+    if (B * H == 0) return 0;
+    EncBatch b{};
+    b.t[0] = enc_tensor(k_cache, k_new, kp, k_tail, k_ckpt);
+    b.t[1] = enc_tensor(v_cache, v_new, vp, v_tail, v_ckpt);
+    return launch_append(b, 2, B, H, T, n_super_cap, bits, scale_min, scale_max, stream,
+                         CkptSpec{interval, n_ckpt_cap});
 }
 
 }  // extern "C"

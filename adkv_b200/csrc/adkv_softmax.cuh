@@ -1,0 +1,110 @@
+// Pieces shared by the fused decode kernels: the logits ring between the K and V warp of a stream, the
+// K-side sink that fills it and the V-side source that turns logits into online-softmax weights.
+#pragma once
+#include "adkv_decode.cuh"
+
+namespace adkv {
+
+template <int G>
+struct FusedShared {
+    float lring[kLogitSlots][G][kTileTok];
+    uint64_t lfull[kLogitSlots], lempty[kLogitSlots];
+};
+
+template <int G>
+struct RingSink {
+    FusedShared<G> *sh;
+    int slot;
+    __device__ __forceinline__ bool begin_tile(int i)
+    {
+        slot = i % kLogitSlots;
+        return mbar_wait_bounded(&sh->lempty[slot], ((i / kLogitSlots) & 1) ^ 1, kStatLEmptyWait);
+    }
+    __device__ __forceinline__ void put8(int, int g, int tok, float v, int lane)
+    {
+        if (lane < 8) sh->lring[slot][g][tok + lane] = v;
+    }
+    __device__ __forceinline__ void end_tile(int, int lane)
+    {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->lfull[slot]);
+    }
+    __device__ __forceinline__ void put_self(int g, float v) { sh->lring[slot][g][0] = v; }
+    __device__ __forceinline__ void finish(int lane) { end_tile(0, lane); }
+};
+
+template <int G>
+struct SoftmaxSrc {
+    FusedShared<G> *sh;
+    float *wts;            // [G][32]
+    const float *mask;     // row of this batch or nullptr
+    float scale2;          // scaling * log2(e)
+    int n_tiles;           // tiles of this segment
+    int t_begin;           // first token of this segment (mask index of local token 0)
+    float m[G], l[G];
+
+    __device__ __forceinline__ void init()
+    {
+#pragma unroll
+        for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+    }
+    // online-softmax update of head g with this lane's logit v (already in log2 units, -inf if invalid)
+    __device__ __forceinline__ float update(int g, float v, float (&acc)[G][4])
+    {
+        const float m_new = fmaxf(m[g], warp_max(v));
+        const bool dead = (m_new == -INFINITY);
+        const float corr = dead ? 1.f : exp2f(m[g] - m_new);
+        const float pw = dead ? 0.f : exp2f(v - m_new);
+        l[g] = fmaf(l[g], corr, warp_sum(pw));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[g][c] *= corr;
+        m[g] = m_new;
+        return pw;
+    }
+    __device__ __forceinline__ bool tile_weights(int i, int ntok, int lane, float (&acc)[G][4])
+    {
+        const int slot = i % kLogitSlots;
+        const float mk = (mask && lane < ntok) ? mask[t_begin + i * kTileTok + lane] * 1.4426950408889634f : 0.f;
+        if (!mbar_wait_bounded(&sh->lfull[slot], (i / kLogitSlots) & 1, kStatLFullWait)) return false;
+        float x[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) x[g] = sh->lring[slot][g][lane];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->lempty[slot]);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float v = lane < ntok ? fmaf(x[g], scale2, mk) : -INFINITY;
+            wts[g * kTileTok + lane] = update(g, v, acc);
+        }
+        __syncwarp();
+        return true;
+    }
+    __device__ __forceinline__ bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
+    {
+        const int slot = n_tiles % kLogitSlots;
+        if (!mbar_wait_bounded(&sh->lfull[slot], (n_tiles / kLogitSlots) & 1, kStatLFullWait)) return false;
+        const float mk = mask ? mask[T] * 1.4426950408889634f : 0.f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float v = fmaf(sh->lring[slot][g][0], scale2, mk);
+            // all lanes hold the same v: update() would count it 32 times, so do it by hand
+            const float m_new = fmaxf(m[g], v);
+            const bool dead = (m_new == -INFINITY);
+            const float corr = dead ? 1.f : exp2f(m[g] - m_new);
+            const float pw = dead ? 0.f : exp2f(v - m_new);
+            l[g] = fmaf(l[g], corr, pw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[g][c] *= corr;
+            m[g] = m_new;
+            w_self[g] = pw;
+        }
+        return true;
+    }
+    __device__ __forceinline__ float norm(int g) const { return l[g]; }
+    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int lane, const float (&acc)[G][4]) const
+    {
+        store_normalised<G>(*this, a, b, h, lane, acc);
+    }
+};
+
+}  // namespace adkv

@@ -1,0 +1,170 @@
+// Part of libadkv_b200.so (sm_100a).  See include/adkv_b200.h for the contract of every entry point.
+//
+// Decode over a checkpointed cache: with the recurrence state stored every `interval` tokens, the
+// segments between checkpoints are independent, so every (stream, segment) gets its own K/V warp
+// pair instead of one pair walking the whole sequence.  Segments leave un-normalised partial results
+// (running maximum, denominator, weighted sums) in caller-provided scratch memory; a second small
+// kernel merges them.  The idea of boundary state checkpoints is the reference paper's (appendix on
+// long contexts); the reference code has no implementation of it.
+#include "adkv_host.h"
+
+#include "adkv_softmax.cuh"
+
+namespace adkv {
+
+constexpr int kPartStride = 4 + kD;   // floats per (stream, segment, head): max (log2 units), denominator, 2 pad, kD sums
+
+template <int G>
+struct PartialSrc : SoftmaxSrc<G> {
+    float *part;   // [G][kPartStride] of this (stream, segment)
+    __device__ __forceinline__ void store(const VArgs &, int, int, int lane, const float (&acc)[G][4]) const
+    {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (lane == 0) {
+                part[g * kPartStride] = this->m[g];
+                part[g * kPartStride + 1] = this->l[g];
+            }
+            *reinterpret_cast<float4 *>(part + g * kPartStride + 4 + 4 * lane) =
+                make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        }
+    }
+};
+
+struct CkptArgs {
+    float *k_ckpt, *v_ckpt;   // [B*Hkv][n_ckpt_cap][2][kD]; entry k = state before token (k+1)*interval
+    int interval, n_ckpt_cap;
+};
+
+template <int BITS, int G, bool EXACT>
+__global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
+                                                               long long mask_stride_b, float scaling, CkptArgs ck,
+                                                               float *__restrict__ scratch)
+{
+    __shared__ alignas(128) uint8_t kbuf[kStages * Tile<BITS>::BYTES];
+    __shared__ alignas(128) uint8_t vbuf[kStages * Tile<BITS>::BYTES];
+    __shared__ alignas(16) float red[8 * 36];
+    __shared__ alignas(16) float wts[G * kTileTok];
+    __shared__ FusedShared<G> fs;
+    __shared__ uint64_t kbar[kStages], vbar[kStages];
+
+    const int bh = blockIdx.x, b = bh / ka.Hkv, h = bh % ka.Hkv;
+    const int j = blockIdx.y, n_seg = gridDim.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) { mbar_init(&kbar[i], 1); mbar_init(&vbar[i], 1); }
+        for (int i = 0; i < kLogitSlots; ++i) { mbar_init(&fs.lfull[i], 1); mbar_init(&fs.lempty[i], 1); }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const int T = ka.T;
+    Seg seg;
+    seg.t_begin = j * ck.interval;
+    seg.t_end = min(T, (j + 1) * ck.interval);
+    seg.append = (j == n_seg - 1);
+    const size_t stream_ckpt = size_t(bh) * ck.n_ckpt_cap;
+    const bool write_ckpt = seg.append && (T + 1) % ck.interval == 0;
+    const size_t out_idx = write_ckpt ? stream_ckpt + (T + 1) / ck.interval - 1 : 0;
+    if (warp == 0) {
+        seg.init = j ? ck.k_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
+        seg.ckpt_out = write_ckpt ? ck.k_ckpt + out_idx * 2 * kD : nullptr;
+        RingSink<G> sink{&fs, 0};
+        k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
+    } else {
+        seg.init = j ? ck.v_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
+        seg.ckpt_out = write_ckpt ? ck.v_ckpt + out_idx * 2 * kD : nullptr;
+        PartialSrc<G> src;
+        src.sh = &fs;
+        src.wts = wts;
+        src.mask = mask ? mask + size_t(b) * mask_stride_b : nullptr;
+        src.scale2 = scaling * 1.4426950408889634f;
+        src.n_tiles = (seg.t_end - seg.t_begin + kTileTok - 1) / kTileTok;
+        src.t_begin = seg.t_begin;
+        src.part = scratch + (size_t(bh) * n_seg + j) * G * kPartStride;
+        src.init();
+        v_warp<BITS, G, EXACT>(va, seg, b, h, lane, vbuf, vbar, wts, src);
+    }
+}
+
+// out[b, hq, c] = sum_j acc_j[c] * 2^(m_j - M) / sum_j l_j * 2^(m_j - M),  M = max_j m_j.
+__global__ void __launch_bounds__(kD) merge_partials_kernel(const float *__restrict__ scratch, __half *__restrict__ out,
+                                                            int Hq, int Hkv, int n_seg)
+{
+    const int bhq = blockIdx.x, b = bhq / Hq, hq = bhq % Hq, G = Hq / Hkv, h = hq / G, g = hq % G;
+    const int c = threadIdx.x;
+    const float *base = scratch + (size_t(b * Hkv + h) * n_seg * G + g) * kPartStride;
+    const size_t seg_stride = size_t(G) * kPartStride;
+    float M = -INFINITY;
+    for (int j = 0; j < n_seg; ++j) M = fmaxf(M, base[j * seg_stride]);
+    float L = 0.f, A = 0.f;
+    for (int j = 0; j < n_seg; ++j) {
+        const float m = base[j * seg_stride];
+        const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+        L = fmaf(base[j * seg_stride + 1], w, L);
+        A = fmaf(base[j * seg_stride + 4 + c], w, A);
+    }
+    out[size_t(bhq) * kD + c] = __float2half_rn(A / L);
+}
+
+}  // namespace adkv
+
+using namespace adkv;
+
+// Status word of this translation unit (read and cleared by adkv_device_status).
+ADKV_HIDDEN int adkv_tu_status_split(int *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
+    if (e != cudaSuccess) return int(e);
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return e == cudaSuccess ? 0 : int(e);
+}
+
+extern "C" {
+
+long long adkv_decode_attn_ckpt_scratch_bytes(int B, int Hq, int Hkv, int T, int interval)
+{
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || T < 0 || interval <= 0 || Hq % Hkv != 0) return ADKV_E_SHAPE;
+    return (long long)B * Hq * (T / interval + 1) * kPartStride * (long long)sizeof(float);
+}
+
+int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                          const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt, int interval,
+                          int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out, void *scratch,
+                          long long scratch_bytes, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
+                          float scaling, float scale_min, float scale_max, unsigned flags, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !params_ok(kp) || !params_ok(vp) || !scratch ||
+        !k_ckpt || !v_ckpt)
+        return ADKV_E_NULL;
+    if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (interval <= 0 || interval % kTileTok != 0 || n_ckpt_cap < 0) return ADKV_E_SHAPE;
+    if ((T + 1) / interval > n_ckpt_cap) return ADKV_E_CAPACITY;
+    if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
+        !aligned8(v_new) || !params_aligned(kp) || !params_aligned(vp) || !aligned16(k_ckpt) || !aligned16(v_ckpt) ||
+        !aligned16(scratch))
+        return ADKV_E_ALIGN;
+    if (scratch_bytes < adkv_decode_attn_ckpt_scratch_bytes(B, Hq, Hkv, T, interval)) return ADKV_E_SCRATCH;
+    if (B == 0) return 0;
+    const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+    const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
+                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+    const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    const int n_seg = T / interval + 1;
+    if (n_seg > 65535) return ADKV_E_SHAPE;
+    const dim3 grid(B * Hkv, n_seg);
+    ADKV_DISPATCH(bits, exact, Hq / Hkv,
+                  (decode_attn_split_kernel<BITS, G, EXACT><<<grid, 64, 0, s>>>(
+                      ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, ck,
+                      static_cast<float *>(scratch))))
+    if (int rc = launch_status()) return rc;
+    merge_partials_kernel<<<B * Hq, kD, 0, s>>>(static_cast<const float *>(scratch), static_cast<__half *>(out), Hq,
+                                               Hkv, n_seg);
+    return launch_status();
+}
+
+}  // extern "C"

@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs k
 #pragma unroll
     for (int g = 0; g < G; ++g) sink.row[g] = logits + (size_t(b) * ka.Hq + size_t(h) * G + g) * (ka.T + 1);
     sink.T = ka.T;
-    k_warp<BITS, G, EXACT>(ka, b, h, lane, kbuf[warp], kbar[warp], red[warp], sink);
+    const Seg seg{0, ka.T, true, nullptr, nullptr};
+    k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf[warp], kbar[warp], red[warp], sink);
 }
 
 template <int G>
@@ -68,6 +69,10 @@ struct GlobalWeightSrc {
         return true;
     }
     __device__ __forceinline__ float norm(int) const { return 1.f; }
+    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int lane, const float (&acc)[G][4]) const
+    {
+        store_normalised<G>(*this, a, b, h, lane, acc);
+    }
 };
 
 template <int BITS, int G, bool EXACT>
@@ -90,7 +95,8 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_ov_kernel(VArgs v
 #pragma unroll
     for (int g = 0; g < G; ++g) src.row[g] = attn + (size_t(b) * va.Hq + size_t(h) * G + g) * (va.T + 1);
     src.wts = wts[warp];
-    v_warp<BITS, G, EXACT>(va, b, h, lane, vbuf[warp], vbar[warp], wts[warp], src);
+    const Seg seg{0, va.T, true, nullptr, nullptr};
+    v_warp<BITS, G, EXACT>(va, seg, b, h, lane, vbuf[warp], vbar[warp], wts[warp], src);
 }
 
 }  // namespace adkv

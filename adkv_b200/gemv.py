@@ -25,7 +25,7 @@ import torch
 from . import _lib
 
 __all__ = ["encode_kv", "forward_qk", "forward_ov", "decode_attn", "append_kv", "encode_kv_pair",
-           "append_kv_pair", "n_super_for"]
+           "append_kv_pair", "n_super_for", "alloc_ckpt", "ckpt_capacity", "decode_scratch_bytes"]
 
 
 def n_super_for(tokens: int, bits: int = 4) -> int:
@@ -91,6 +91,27 @@ def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min
     return kv_cache
 
 
+def ckpt_capacity(tokens: int, interval: int) -> int:
+    """Checkpoints a cache of ``tokens`` tokens can reach (entry k = state before token (k+1)*interval)."""
+    return tokens // interval
+
+
+def alloc_ckpt(B: int, H: int, D: int, capacity_tokens: int, interval: int, device) -> torch.Tensor:
+    """Checkpoint tensor ``[B, H, n_ckpt_cap, 2, D]`` float32 for caches of up to ``capacity_tokens`` tokens."""
+    return torch.zeros((B, H, max(1, ckpt_capacity(capacity_tokens, interval)), 2, D), dtype=torch.float32,
+                       device=device)
+
+
+def _ckpt_args(k_ckpt, v_ckpt, interval, B, H, D):
+    _require(k_ckpt is not None and v_ckpt is not None, "both checkpoint tensors are needed")
+    _require(interval > 0 and interval % 32 == 0, "checkpoint interval must be a positive multiple of 32")
+    for c in (k_ckpt, v_ckpt):
+        _require(c.dtype == torch.float32 and c.is_contiguous() and c.dim() == 5 and c.shape[0] == B and
+                 c.shape[1] == H and c.shape[3] == 2 and c.shape[4] == D and c.shape[2] == k_ckpt.shape[2],
+                 "checkpoints must be contiguous float32 [B, nh, n_ckpt_cap, 2, DIM]")
+    return k_ckpt.data_ptr(), v_ckpt.data_ptr(), interval, k_ckpt.shape[2]
+
+
 def _tail_ptr(tail, B, H, D):
     if tail is None:
         return None
@@ -100,9 +121,10 @@ def _tail_ptr(tail, B, H, D):
 
 
 def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min, scale_max, *, bits: int = 4,
-                   k_tail=None, v_tail=None, t_start: int = 0):
+                   k_tail=None, v_tail=None, t_start: int = 0, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0):
     """``encode_kv`` for the K and V tensors of one layer in a single launch (same contract each;
-    replaces the two calls of ``src/adkv/hf/llama_adkv.py:144-153``)."""
+    replaces the two calls of ``src/adkv/hf/llama_adkv.py:144-153``).  With ``k_ckpt`` / ``v_ckpt`` /
+    ``ckpt_interval`` every state checkpoint reached is written as well (see :func:`alloc_ckpt`)."""
     _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "kv_new must be float16")
     B, H, n_super_cap, D = _cache_dims(k_cache, "kv_cache")
     _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
@@ -120,17 +142,25 @@ def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
     with torch.cuda.device(k_cache.device):
-        rc = _lib.load().adkv_encode_kv(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
-                                        _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
-                                        ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D, n_super_cap,
-                                        bits, t_start, scale_min, scale_max, _stream(k_cache))
+        if ckpt_interval:
+            kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D)
+            rc = _lib.load().adkv_encode_kv_ckpt(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                                 _tail_ptr(k_tail, B, H, D), kc, v_cache.data_ptr(), xv.data_ptr(),
+                                                 ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), vc, iv, cap,
+                                                 B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max,
+                                                 _stream(k_cache))
+        else:
+            rc = _lib.load().adkv_encode_kv(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                            _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
+                                            ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D,
+                                            n_super_cap, bits, t_start, scale_min, scale_max, _stream(k_cache))
     _lib.check(rc, "encode_kv_pair")
     return k_cache, v_cache
 
 
 def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v_tail, T: int, scale_min, scale_max,
-                   *, bits: int = 4):
-    """``append_kv`` for K and V of one layer in a single launch."""
+                   *, bits: int = 4, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0):
+    """``append_kv`` for K and V of one layer in a single launch (optionally maintaining state checkpoints)."""
     B, H, n_super_cap, D = _cache_dims(k_cache, "cache")
     _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
              "v_cache must match k_cache")
@@ -145,10 +175,18 @@ def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
     with torch.cuda.device(k_cache.device):
-        rc = _lib.load().adkv_append_kv(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
-                                        _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
-                                        ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D, n_super_cap,
-                                        bits, scale_min, scale_max, _stream(k_cache))
+        if ckpt_interval:
+            kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D)
+            rc = _lib.load().adkv_append_kv_ckpt(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                                 _tail_ptr(k_tail, B, H, D), kc, v_cache.data_ptr(), xv.data_ptr(),
+                                                 ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), vc, iv, cap,
+                                                 B, H, T, D, n_super_cap, bits, scale_min, scale_max,
+                                                 _stream(k_cache))
+        else:
+            rc = _lib.load().adkv_append_kv(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                            _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
+                                            ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D,
+                                            n_super_cap, bits, scale_min, scale_max, _stream(k_cache))
     _lib.check(rc, "append_kv_pair")
     return k_cache, v_cache
 
@@ -234,16 +272,28 @@ def forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min
     return o
 
 
+def decode_scratch_bytes(B: int, Hq: int, Hkv: int, T: int, interval: int) -> int:
+    """Scratch bytes the checkpointed decode step needs for a cache of ``T`` tokens."""
+    n = _lib.load().adkv_decode_attn_ckpt_scratch_bytes(B, Hq, Hkv, T, interval)
+    _lib.check(min(n, 0), "decode_scratch_bytes")
+    return n
+
+
 def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
                 scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False,
-                out: torch.Tensor | None = None):
+                out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0,
+                scratch: torch.Tensor | None = None):
     """Fused decode step over both packed caches.
 
     ``q [B, nh_q, 1, DIM]``, ``k_new`` / ``v_new [B, nh_kv, 1, DIM]`` float16; ``k_params`` / ``v_params``
     the five ``[nh_kv, DIM]`` float16 tensors (zp_init, scale_init, alpha, beta, target); ``mask`` an
     additive ``[B, T+1]`` (or ``[B, 1, T+1]`` / ``[B, 1, 1, T+1]``) tensor shared by all heads.  Appends to
     both caches in place as token ``T`` and returns ``softmax(q.K^T * scaling + mask) . V`` as
-    ``[B, nh_q, DIM]`` float16, the appended token included (``src/adkv/hf/llama_adkv.py:263-276``)."""
+    ``[B, nh_q, DIM]`` float16, the appended token included (``src/adkv/hf/llama_adkv.py:263-276``).
+
+    With state checkpoints (``k_ckpt``, ``v_ckpt``, ``ckpt_interval``; see :func:`alloc_ckpt`) the token axis is
+    processed in independent segments; ``scratch`` (uint8/any dtype, at least :func:`decode_scratch_bytes`) is
+    allocated per call when not given."""
     _require(q.dtype == torch.float16, "q must be float16")
     _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "k_new / v_new must be float16")
     B, Hkv, n_super_cap, D = _cache_dims(k_cache, "k_cache")
@@ -271,12 +321,26 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
     else:
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
+    flags = _lib.FLAG_FAST_REPLAY if fast else 0
     with torch.cuda.device(k_cache.device):
-        rc = _lib.load().adkv_decode_attn(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
-                                          vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp), mptr, mstride,
-                                          out.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scaling,
-                                          scale_min, scale_max, _lib.FLAG_FAST_REPLAY if fast else 0,
-                                          _stream(k_cache))
+        if ckpt_interval:
+            kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, Hkv, D)
+            need = decode_scratch_bytes(B, Hq, Hkv, T, iv)
+            if scratch is None:
+                scratch = torch.empty(need, dtype=torch.uint8, device=k_cache.device)
+            _require(scratch.is_cuda and scratch.is_contiguous(), "scratch must be a contiguous CUDA tensor")
+            rc = _lib.load().adkv_decode_attn_ckpt(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                   kn.data_ptr(), vn.data_ptr(), ctypes.addressof(kp),
+                                                   ctypes.addressof(vp), kc, vc, iv, cap, mptr, mstride,
+                                                   out.data_ptr(), scratch.data_ptr(),
+                                                   scratch.numel() * scratch.element_size(), B, Hq, Hkv, T, D,
+                                                   n_super_cap, bits, scaling, scale_min, scale_max, flags,
+                                                   _stream(k_cache))
+        else:
+            rc = _lib.load().adkv_decode_attn(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
+                                              vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp), mptr,
+                                              mstride, out.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scaling,
+                                              scale_min, scale_max, flags, _stream(k_cache))
     _lib.check(rc, "decode_attn")
     return out
 

@@ -241,7 +241,7 @@ def run_reference(args, w, name):
 
 # --------------------------------------------------------------------------------------- GPU arm
 
-def build_gpu_state(w, seed, device, torch):
+def build_gpu_state(w, seed, device, torch, ckpt_interval=0):
     """Caches prefilled by the encode kernel from on-device synthetic K/V, plus the step's inputs."""
     from adkv_b200 import gemv, synth
     B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
@@ -250,19 +250,28 @@ def build_gpu_state(w, seed, device, torch):
     vp = synth.gen_params(seed + 4, Hkv, D, bits, device=device)
     kc = torch.zeros((B, Hkv, ns, D // 4, 4, 4), dtype=torch.uint8, device=device)
     vc = torch.zeros_like(kc)
+    kck = vck = scratch = None
+    if ckpt_interval:
+        kck = gemv.alloc_ckpt(B, Hkv, D, T + 1, ckpt_interval, device)
+        vck = gemv.alloc_ckpt(B, Hkv, D, T + 1, ckpt_interval, device)
+        scratch = torch.empty(gemv.decode_scratch_bytes(B, Hq, Hkv, T, ckpt_interval), dtype=torch.uint8, device=device)
     chunk = max(1, min(B, (1 << 28) // (Hkv * T * D)))      # keep generator temporaries around 1 GiB
     for b0 in range(0, B, chunk):
         b1 = min(B, b0 + chunk)
         k = synth.gen_kv(seed + 10 * b0, b1 - b0, Hkv, T, D, device=device)
-        gemv.encode_kv(kc[b0:b1], k, *kp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
         v = synth.gen_kv(seed + 10 * b0 + 1, b1 - b0, Hkv, T, D, device=device)
-        gemv.encode_kv(vc[b0:b1], v, *vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+        if ckpt_interval:
+            gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits,
+                                k_ckpt=kck[b0:b1], v_ckpt=vck[b0:b1], ckpt_interval=ckpt_interval)
+        else:
+            gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
         del k, v
     q = synth.gen_q(seed + 2, B, Hq, D, device=device)
     kn = synth.gen_kv(seed + 5, B, Hkv, 1, D, device=device, pos0=T)
     vn = synth.gen_kv(seed + 6, B, Hkv, 1, D, device=device, pos0=T)
     torch.cuda.synchronize(device)
-    return dict(kc=kc, vc=vc, kp=kp, vp=vp, q=q, kn=kn, vn=vn)
+    ck = dict(k_ckpt=kck, v_ckpt=vck, ckpt_interval=ckpt_interval, scratch=scratch) if ckpt_interval else {}
+    return dict(kc=kc, vc=vc, kp=kp, vp=vp, q=q, kn=kn, vn=vn, ck=ck)
 
 
 def check_against_oracle(w, st, out, n_streams, torch):
@@ -429,7 +438,8 @@ def run_ours(args, w, name):
     if args.scaling == "strong" and world > 1:
         assert w["B"] % world == 0, "strong scaling splits the batch evenly"
         w["B"] //= world
-    st = build_gpu_state(w, seed=1000 + 7919 * rank, device=device, torch=torch)
+    st = build_gpu_state(w, seed=1000 + 7919 * rank, device=device, torch=torch, ckpt_interval=args.ckpt_interval)
+    ck = st["ck"]
     B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
     scaling = D ** -0.5
     fast = args.replay == "fast"
@@ -437,7 +447,7 @@ def run_ours(args, w, name):
 
     def step():
         gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out, **ck)
 
     def barrier():
         if world > 1:
@@ -478,7 +488,7 @@ def run_ours(args, w, name):
         dk_.copy_(hk, non_blocking=True)
         dv_.copy_(hv, non_blocking=True)
         gemv.decode_attn(dq, st["kc"], st["vc"], dk_, dv_, st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out, **ck)
         hout.copy_(out, non_blocking=True)
 
     for _ in range(max(3, min(args.warmup, 5))):
@@ -500,7 +510,7 @@ def run_ours(args, w, name):
         if it == 3:
             o0.record()
         gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=other, out=out)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=other, out=out, **ck)
     o1.record()
     barrier()
     other_ms = o0.elapsed_time(o1) / other_steps
@@ -525,12 +535,13 @@ def run_ours(args, w, name):
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload=name, per_gpu=w, global_batch=w["B"] * world, replay=args.replay,
+                           ckpt_interval=args.ckpt_interval,
                            sharding="batch, one process per GPU, no collective on the data path",
                            l2="inputs (packed K+V per step) larger than L2; no flush needed"
                            if bytes_rank > 200e6 else "inputs smaller than L2: cache-resident timing"),
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": world * (hq.numel() + hk.numel() + hv.numel()) * 2,
                     "d2h_bytes_per_step": world * hout.numel() * 2, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (2 if args.ckpt_interval else 1),
             "decode_tokens_per_s": {"one_layer": w["B"] * world * args.steps / (total_ms * 1e-3),
                                     "over_32_layers": w["B"] * world * args.steps / (total_ms * 1e-3) / 32},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -567,6 +578,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--replay", choices=["exact", "fast"], default="exact")
+    ap.add_argument("--ckpt-interval", type=int, default=0,
+                    help="decode with state checkpoints every N tokens (segment-parallel kernel + merge)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -41,6 +41,7 @@ extern "C" {
 #define ADKV_E_CAPACITY  (-5)  /* the cache has no room for the tokens to be written */
 #define ADKV_E_ALIGN     (-6)  /* a pointer is not 16-byte aligned */
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
+#define ADKV_E_SCRATCH   (-8)  /* the scratch memory given is smaller than the problem needs */
 
 /* flags */
 #define ADKV_FLAG_FAST_REPLAY 1u  /* decode kernels: contracted (FMA) replay of cached tokens */
@@ -116,6 +117,37 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
                      const adkv_params *kp, const adkv_params *vp, const void *mask, long long mask_stride_b,
                      void *out, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
                      float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
+
+/* ---- State checkpoints (opt-in; no counterpart in the reference's code, proposed in its paper for long
+ * contexts).  A checkpoint tensor float [B, H, n_ckpt_cap, 2, D] per cache holds, in entry k, the recurrence
+ * state (zp then scale) before token (k+1)*interval; `interval` is a multiple of 32.  With them the token
+ * axis splits into independent segments: 8 bytes per channel per `interval` tokens buy `T/interval + 1`
+ * times the parallelism, which is what small-batch long-context decode lacks. */
+
+/* adkv_encode_kv that also writes every checkpoint reached in [t_start, t_start+T]. */
+int adkv_encode_kv_ckpt(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                        void *v_cache, const void *v, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                        int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                        int t_start, float scale_min, float scale_max, void *stream);
+
+/* adkv_append_kv that also writes the checkpoint when token T completes an interval. */
+int adkv_append_kv_ckpt(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                        void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                        int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                        float scale_min, float scale_max, void *stream);
+
+/* Bytes of scratch adkv_decode_attn_ckpt needs (negative: ADKV_E_*). */
+long long adkv_decode_attn_ckpt_scratch_bytes(int B, int Hq, int Hkv, int T, int interval);
+
+/* adkv_decode_attn over a checkpointed cache: one K/V warp pair per (stream, segment), partial results in
+ * `scratch` (caller-owned device memory of at least adkv_decode_attn_ckpt_scratch_bytes, 16-byte aligned,
+ * contents irrelevant on entry), then a merge kernel.  Appends token T to both caches and writes the
+ * checkpoint when T completes an interval.  Same result as adkv_decode_attn up to fp32 summation order. */
+int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                          const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt, int interval,
+                          int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out, void *scratch,
+                          long long scratch_bytes, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
+                          float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
 
 /* Reads and clears the device-side status word of the current device (HOST pointer `status`;
  * synchronises `stream`).  Non-zero means a kernel gave up on a bounded wait; the value encodes
