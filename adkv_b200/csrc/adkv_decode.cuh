@@ -82,56 +82,61 @@ struct StreamRing {
 // ---------------------------------------------------------------------------------- K side
 
 // Replay 8 tokens (fields 0..7 of the 4 words in `w`; the caller shifts the second half of a 16-token
-// word down) and accumulate the partial dot products.  `count`: valid fields when PARTIAL.
+// word down) and leave the per-lane partial dot products of head g, token j in red[(g*8 + j)*36 + lane].
+// The two halves of 4 tokens run through ONE body in a two-trip loop, which halves the straight-line
+// code (with several query heads per KV head the unrolled body no longer fitted the instruction
+// cache).  `count`: valid fields when PARTIAL (the others are stored as zero).
 template <int BITS, int G, bool EXACT, bool PARTIAL, bool GUARDED>
 __device__ __forceinline__ void k_chunk(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
-                                        const float (&qv)[G][4], float (&part)[G][8], int count, float smin,
+                                        const float (&qv)[G][4], float *red, int lane, int count, float smin,
                                         float smax)
 {
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    uint32_t lo[4], hi[4];
+    uint32_t grp[4] = {w.x, w.y, w.z, w.w};
+    // one query head: both halves unrolled (measured faster); several heads: one body, two trips
+#pragma unroll(G == 1 ? 2 : 1)
+    for (int half = 0; half < 2; ++half) {
+        static_for<4>([&](auto kc) {
+            constexpr int k = decltype(kc)::value;
+            float part[G];
+            if (!PARTIAL || 4 * half + k < count) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        lo[c] = ww[c];
-        hi[c] = ww[c] >> (4 * BITS);
-    }
-    static_for<8>([&](auto jc) {
-        constexpr int j = decltype(jc)::value;
-        if (!PARTIAL || j < count) {
+                for (int c = 0; c < 4; ++c) {
+                    const float q = fc.template code<k>(grp[c]);
+                    const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float q = fc.template code<j % 4>(j < 4 ? lo[c] : hi[c]);
-                const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
+                    for (int g = 0; g < G; ++g) part[g] = c == 0 ? qv[g][0] * xh : fmaf(qv[g][c], xh, part[g]);
+                }
+            } else {
 #pragma unroll
-                for (int g = 0; g < G; ++g) part[g][j] = c == 0 ? qv[g][0] * xh : fmaf(qv[g][c], xh, part[g][j]);
+                for (int g = 0; g < G; ++g) part[g] = 0.f;
             }
-        } else {
 #pragma unroll
-            for (int g = 0; g < G; ++g) part[g][j] = 0.f;
-        }
-    });
+            for (int g = 0; g < G; ++g) red[(g * 8 + 4 * half + k) * 36 + lane] = part[g];
+        });
+#pragma unroll
+        for (int c = 0; c < 4; ++c) grp[c] >>= 4 * BITS;
+    }
 }
 
-// Sum part[g][0..7] over the 32 lanes through a shared-memory transpose; afterwards lane l
+// Sum the partials left by k_chunk over the 32 lanes: each lane reads 8 lanes' values of one token
+// (two 16-byte loads from the padded transpose) and two shuffles finish the job; afterwards lane l
 // (every lane, replicated over l>>3) holds the full sum for token (l & 7) of head g.
-// red: float [8][36] of this warp, reused head after head.
+// red: float [G][8][36] of this warp.
 template <int G>
-__device__ __forceinline__ void reduce8(float (&part)[G][8], float *red, int lane, float (&sum)[G])
+__device__ __forceinline__ void reduce8(const float *red, int lane, float (&sum)[G])
 {
+    __syncwarp();
     const int row = lane & 7, cb = (lane >> 3) * 8;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) red[j * 36 + lane] = part[g][j];
-        __syncwarp();
-        const float4 a = *reinterpret_cast<const float4 *>(&red[row * 36 + cb]);
-        const float4 b = *reinterpret_cast<const float4 *>(&red[row * 36 + cb + 4]);
-        __syncwarp();
+        const float4 a = *reinterpret_cast<const float4 *>(&red[(g * 8 + row) * 36 + cb]);
+        const float4 b = *reinterpret_cast<const float4 *>(&red[(g * 8 + row) * 36 + cb + 4]);
         float s = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
         s += __shfl_xor_sync(kFull, s, 8);
         s += __shfl_xor_sync(kFull, s, 16);
         sum[g] = s;
     }
+    __syncwarp();
 }
 
 // The part of a stream one warp pair works on.  The whole-stream kernels use {0, T, true, nullptr, nullptr};
@@ -204,7 +209,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
         if (!(ok = sink.begin_tile(i))) break;
         const uint4 *tile = ring.tile(i, lane);
         const int ntok = min(kTileTok, n_tok - i * kTileTok);
-        float part[G][8], sum[G];
+        float sum[G];
         if (ntok == kTileTok) {
             // not unrolled over the words of the tile: the loop body must stay resident in the
             // instruction cache while K and V warps of many streams interleave
@@ -214,9 +219,9 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
                 const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
-                    if (safe.holds(ch)) k_chunk<BITS, G, EXACT, false, false>(w, fc, ch, qv, part, 8, a.smin, a.smax);
-                    else k_chunk<BITS, G, EXACT, false, true>(w, fc, ch, qv, part, 8, a.smin, a.smax);
-                    reduce8<G>(part, red, lane, sum);
+                    if (safe.holds(ch)) k_chunk<BITS, G, EXACT, false, false>(w, fc, ch, qv, red, lane, 8, a.smin, a.smax);
+                    else k_chunk<BITS, G, EXACT, false, true>(w, fc, ch, qv, red, lane, 8, a.smin, a.smax);
+                    reduce8<G>(red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
                     if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
@@ -230,8 +235,8 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
                 const int count = ntok - wd * C::TPW;   // valid fields in this word (may exceed TPW)
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
-                    k_chunk<BITS, G, EXACT, true, true>(w, fc, ch, qv, part, count - c8 * 8, a.smin, a.smax);
-                    reduce8<G>(part, red, lane, sum);
+                    k_chunk<BITS, G, EXACT, true, true>(w, fc, ch, qv, red, lane, count - c8 * 8, a.smin, a.smax);
+                    reduce8<G>(red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
                     if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
@@ -284,33 +289,31 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> 
                                         const float *wts /* [G][32] smem */, int tok0, float (&acc)[G][4],
                                         int count, float smin, float smax)
 {
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    uint32_t lo[4], hi[4];
+    uint32_t grp[4] = {w.x, w.y, w.z, w.w};
+    // one query head: both halves unrolled (measured faster); several heads: one body, two trips
+#pragma unroll(G == 1 ? 2 : 1)
+    for (int half = 0; half < 2; ++half) {
+        float wt[G][4];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        lo[c] = ww[c];
-        hi[c] = ww[c] >> (4 * BITS);
-    }
-    float wt[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float4 a = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0);
-        const float4 b = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0 + 4);
-        wt[g][0] = a.x; wt[g][1] = a.y; wt[g][2] = a.z; wt[g][3] = a.w;
-        wt[g][4] = b.x; wt[g][5] = b.y; wt[g][6] = b.z; wt[g][7] = b.w;
-    }
-    static_for<8>([&](auto jc) {
-        constexpr int j = decltype(jc)::value;
-        if (!PARTIAL || j < count) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float q = fc.template code<j % 4>(j < 4 ? lo[c] : hi[c]);
-                const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
-#pragma unroll
-                for (int g = 0; g < G; ++g) acc[g][c] = fmaf(wt[g][j], xh, acc[g][c]);
-            }
+        for (int g = 0; g < G; ++g) {
+            const float4 a = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0 + 4 * half);
+            wt[g][0] = a.x; wt[g][1] = a.y; wt[g][2] = a.z; wt[g][3] = a.w;
         }
-    });
+        static_for<4>([&](auto kc) {
+            constexpr int k = decltype(kc)::value;
+            if (!PARTIAL || 4 * half + k < count) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float q = fc.template code<k>(grp[c]);
+                    const float xh = replay_step<EXACT, GUARDED>(q, ch[c], smin, smax);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) acc[g][c] = fmaf(wt[g][k], xh, acc[g][c]);
+                }
+            }
+        });
+#pragma unroll
+        for (int c = 0; c < 4; ++c) grp[c] >>= 4 * BITS;
+    }
 }
 
 struct VArgs {

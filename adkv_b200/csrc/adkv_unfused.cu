@@ -7,9 +7,9 @@
 namespace adkv {
 
 // =========================================================================================
-// Unfused entry points (the reference's two-kernel decode): 4 streams per CTA, one warp each.
+// Unfused entry points (the reference's two-kernel decode): 2 streams per CTA, one warp each.
 
-constexpr int kStreamsPerCta = 4;
+constexpr int kStreamsPerCta = 2;
 
 template <int G>
 struct GlobalLogitSink {
@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs k
                                                                          int n_streams)
 {
     __shared__ alignas(128) uint8_t kbuf[kStreamsPerCta][kStages * Tile<BITS>::BYTES];
-    __shared__ alignas(16) float red[kStreamsPerCta][8 * 36];
+    __shared__ alignas(16) float red[kStreamsPerCta][G * 8 * 36];
     __shared__ uint64_t kbar[kStreamsPerCta][kStages];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) {
