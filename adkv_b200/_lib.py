@@ -31,6 +31,9 @@ SIGNATURES = {
     "adkv_decode_attn_ckpt": [c_void_p] * 9 + [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_uint,
                               c_void_p],
+    "adkv_decode_attn_ckpt_static": [c_void_p] * 9 + [c_int, c_int, c_void_p, c_longlong, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float,
+                                     c_uint, c_void_p],
     "adkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                     c_float, c_float, c_void_p],
     "adkv_forward_qk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

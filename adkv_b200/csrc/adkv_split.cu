@@ -8,6 +8,8 @@
 // long contexts); the reference code has no implementation of it.
 #include "adkv_host.h"
 
+#include <mutex>
+
 #include "adkv_softmax.cuh"
 
 namespace adkv {
@@ -165,6 +167,69 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
     merge_partials_kernel<<<B * Hq, kD, 0, s>>>(static_cast<const float *>(scratch), static_cast<__half *>(out), Hq,
                                                Hkv, n_seg);
     return launch_status();
+}
+
+}  // extern "C"
+
+// =========================================================================================
+// The same decode step for callers that are not in a position to provide scratch memory.
+//
+// Some hosts of this library cannot allocate: an inference server that has handed every byte of HBM
+// to its own block pool at start-up has nothing left for cudaMalloc to give (and would not want the
+// fragmentation), and a plugin that is only ever passed device pointers by its host runtime has no
+// allocator to ask.  For them the partial results live in the fixed array below instead of a
+// caller-owned buffer.  Every process that loads the library pays for the array on every GPU it
+// touches until it exits, which is why it is kept to ADKV_STATIC_SCRATCH_BYTES.
+namespace adkv {
+
+static __device__ __align__(256) float g_static_scratch[ADKV_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: handing it
+// to a kernel would fault or, where the GPU can reach host memory, quietly use the wrong memory.
+// The device address is asked for once per device, with that device current, and remembered.
+constexpr int kMaxDevices = 64;
+static float *g_static_scratch_addr[kMaxDevices];
+static bool g_static_scratch_known[kMaxDevices];
+static std::mutex g_static_scratch_lock;
+
+static int static_scratch_of_current_device(float **addr)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return int(e);
+    if (dev < 0 || dev >= kMaxDevices) return ADKV_E_SHAPE;
+    std::lock_guard<std::mutex> guard(g_static_scratch_lock);
+    if (!g_static_scratch_known[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return int(e);
+        g_static_scratch_addr[dev] = static_cast<float *>(p);
+        g_static_scratch_known[dev] = true;
+    }
+    *addr = g_static_scratch_addr[dev];
+    return 0;
+}
+
+}  // namespace adkv
+
+extern "C" {
+
+int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                                 const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt,
+                                 int interval, int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out,
+                                 int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scaling,
+                                 float scale_min, float scale_max, unsigned flags, void *stream)
+{
+    const long long need = adkv_decode_attn_ckpt_scratch_bytes(B, Hq, Hkv, T, interval);
+    if (need < 0) return int(need);
+    if (need > (long long)ADKV_STATIC_SCRATCH_BYTES) return ADKV_E_STATIC_MAX;
+    float *scratch = nullptr;
+    if (int rc = static_scratch_of_current_device(&scratch)) return rc;
+    // Nothing in the array has to start at zero: the segment kernel writes every slot the merge kernel
+    // reads, so what an earlier call left behind is simply overwritten.
+    return adkv_decode_attn_ckpt(q, k_cache, v_cache, k_new, v_new, kp, vp, k_ckpt, v_ckpt, interval, n_ckpt_cap,
+                                 mask, mask_stride_b, out, scratch, (long long)ADKV_STATIC_SCRATCH_BYTES, B, Hq, Hkv,
+                                 T, D, n_super_cap, bits, scaling, scale_min, scale_max, flags, stream);
 }
 
 }  // extern "C"

@@ -345,6 +345,57 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
     return out
 
 
+STATIC_SCRATCH_BYTES = 16 << 20
+
+
+def decode_attn_static(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
+                       scale_min, scale_max, *, k_ckpt, v_ckpt, ckpt_interval: int, out: torch.Tensor,
+                       mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False):
+    """The checkpointed decode step for a caller that must not allocate device memory.
+
+    Same arguments and result as ``decode_attn(..., k_ckpt=, v_ckpt=, ckpt_interval=)``, except that ``out``
+    is required (nothing is allocated here either) and the partial results go to a 16 MiB array built into the
+    library instead of a scratch tensor.  Use it when the process has no device memory left to give -- all of
+    HBM already belongs to a block pool -- or no allocator to call.  ``decode_scratch_bytes(...)`` must not
+    exceed ``STATIC_SCRATCH_BYTES``, otherwise a ``RuntimeError`` names the limit.  The array is shared by
+    every call on the device and keeps the previous call's contents (harmless: each call overwrites what it
+    reads), so calls that could run concurrently on the GPU must be serialised by the caller.  The first call
+    on a device also looks up the array's address; issue it before starting any stream capture.
+
+    Inputs must already be contiguous float16 / float32 tensors on the cache's device (no copies are made);
+    ``mask``, if given, a contiguous float32 ``[B, T+1]`` tensor."""
+    B, Hkv, n_super_cap, D = _cache_dims(k_cache, "k_cache")
+    Hq = q.shape[1]
+    for name, t, dt in (("q", q, torch.float16), ("k_new", k_new, torch.float16), ("v_new", v_new, torch.float16),
+                        ("out", out, torch.float16)):
+        _require(t.dtype == dt and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous CUDA {dt} tensor")
+    _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda and
+             k_cache.is_contiguous() and v_cache.is_contiguous(), "caches must be matching contiguous uint8 tensors")
+    _require(q.numel() == B * Hq * D and out.numel() == B * Hq * D and Hq % Hkv == 0, "q / out must be [B, nh_q, DIM]")
+    _require(k_new.numel() == B * Hkv * D and v_new.numel() == B * Hkv * D, "k_new / v_new must be [B, nh, 1, DIM]")
+    _require(T >= 0 and T // (32 // bits) < n_super_cap, f"cache has no free supergroup to append token {T}")
+    for name, ps in (("k", k_params), ("v", v_params)):
+        for t in ps:
+            _require(t.dtype == torch.float16 and t.is_cuda and t.is_contiguous() and t.numel() == Hkv * D,
+                     f"{name} parameters must be contiguous float16 [nh, DIM] CUDA tensors")
+    kp = _lib.Params(*[t.data_ptr() for t in k_params])
+    vp = _lib.Params(*[t.data_ptr() for t in v_params])
+    kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, Hkv, D)
+    mptr, mstride = None, 0
+    if mask is not None:
+        _require(mask.dtype == torch.float32 and mask.is_cuda and mask.is_contiguous() and
+                 tuple(mask.shape) == (B, T + 1), "mask must be a contiguous float32 [B, T + 1] CUDA tensor")
+        mptr, mstride = mask.data_ptr(), T + 1
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().adkv_decode_attn_ckpt_static(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+            ctypes.addressof(kp), ctypes.addressof(vp), kc, vc, iv, cap, mptr, mstride, out.data_ptr(),
+            B, Hq, Hkv, T, D, n_super_cap, bits, scaling, scale_min, scale_max,
+            _lib.FLAG_FAST_REPLAY if fast else 0, _stream(k_cache))
+    _lib.check(rc, "decode_attn_static")
+    return out
+
+
 def device_status(device=None) -> int:
     """Read and clear the device status word (non-zero: a kernel gave up on a bounded wait)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

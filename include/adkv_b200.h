@@ -42,6 +42,10 @@ extern "C" {
 #define ADKV_E_ALIGN     (-6)  /* a pointer is not 16-byte aligned */
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
 #define ADKV_E_SCRATCH   (-8)  /* the scratch memory given is smaller than the problem needs */
+#define ADKV_E_STATIC_MAX (-9) /* problem needs more than ADKV_STATIC_SCRATCH_BYTES of built-in scratch */
+
+/* Size of the library's built-in scratch array (see adkv_decode_attn_ckpt_static). */
+#define ADKV_STATIC_SCRATCH_BYTES (16u << 20)
 
 /* flags */
 #define ADKV_FLAG_FAST_REPLAY 1u  /* decode kernels: contracted (FMA) replay of cached tokens */
@@ -148,6 +152,26 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
                           int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out, void *scratch,
                           long long scratch_bytes, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
                           float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
+
+/* adkv_decode_attn_ckpt for callers that cannot allocate device memory.  (No counterpart in the reference:
+ * its wrappers allocate with torch inside every call.)  Meant for hosts whose HBM is entirely owned by their
+ * own pool, or that only ever receive device pointers and have no allocator to call: inputs and outputs are
+ * still the caller's, but the partial results go to a fixed array inside the library instead of a `scratch`
+ * argument, and the call itself allocates nothing (no cudaMalloc/cudaFree, no allocating library routine).
+ *   - Limit: adkv_decode_attn_ckpt_scratch_bytes(B, Hq, Hkv, T, interval) must not exceed
+ *     ADKV_STATIC_SCRATCH_BYTES (16 MiB, i.e. B*Hq*(T/interval+1) <= 31775); larger problems return
+ *     ADKV_E_STATIC_MAX and launch nothing.  The array is resident on every GPU the process uses, from
+ *     library load to exit, whether or not this entry point is ever called.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call outside any stream capture.  Later calls only launch.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call wrote.  Nothing in it
+ *     needs clearing (every slot read is written first within the call), but two calls that overlap on the
+ *     GPU -- different streams, or different host threads -- race on it: serialise them. */
+int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                                 const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt,
+                                 int interval, int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out,
+                                 int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scaling,
+                                 float scale_min, float scale_max, unsigned flags, void *stream);
 
 /* Reads and clears the device-side status word of the current device (HOST pointer `status`;
  * synchronises `stream`).  Non-zero means a kernel gave up on a bounded wait; the value encodes
