@@ -118,6 +118,44 @@ __device__ __forceinline__ void k_chunk(const uint4 &w, const FieldConsts<BITS> 
     }
 }
 
+// The unguarded, full 8-token case of k_chunk on channel pairs (packed fp32): identical results for the
+// state; the per-lane partial dot product is summed in a different order (pairs first).
+template <int BITS, int G, bool EXACT>
+__device__ __forceinline__ void k_chunk2(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
+                                         const PairConst (&pc)[2], const f32x2 (&qv2)[G][2], float *red, int lane)
+{
+    uint32_t grp[4] = {w.x, w.y, w.z, w.w};
+    f32x2 zp[2] = {pk2(ch[0].zp, ch[1].zp), pk2(ch[2].zp, ch[3].zp)};
+    f32x2 s[2] = {pk2(ch[0].s, ch[1].s), pk2(ch[2].s, ch[3].s)};
+    const f32x2 one = opaque_ones2();
+#pragma unroll(G == 1 ? 2 : 1)
+    for (int half = 0; half < 2; ++half) {
+        static_for<4>([&](auto kc) {
+            constexpr int k = decltype(kc)::value;
+            f32x2 part[G];
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const f32x2 q2 = fc.template code2<k>(grp[2 * p], grp[2 * p + 1]);
+                const f32x2 xh = replay_step2<EXACT>(q2, zp[p], s[p], pc[p], one);
+#pragma unroll
+                for (int g = 0; g < G; ++g) part[g] = p == 0 ? mul2(qv2[g][0], xh) : fma2(qv2[g][1], xh, part[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a, b;
+                upk2(part[g], a, b);
+                red[(g * 8 + 4 * half + k) * 36 + lane] = a + b;
+            }
+        });
+#pragma unroll
+        for (int c = 0; c < 4; ++c) grp[c] >>= 4 * BITS;
+    }
+    upk2(zp[0], ch[0].zp, ch[1].zp);
+    upk2(zp[1], ch[2].zp, ch[3].zp);
+    upk2(s[0], ch[0].s, ch[1].s);
+    upk2(s[1], ch[2].s, ch[3].s);
+}
+
 // Sum the partials left by k_chunk over the 32 lanes: each lane reads 8 lanes' values of one token
 // (two 16-byte loads from the padded transpose) and two shuffles finish the job; afterwards lane l
 // (every lane, replicated over l>>3) holds the full sum for token (l & 7) of head g.
@@ -195,6 +233,14 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
     float qv[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane);
+    PairConst pc[2];
+    make_pair_consts<EXACT>(ch, pc);
+    f32x2 qv2[G][2];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        qv2[g][0] = pk2(qv[g][0], qv[g][1]);
+        qv2[g][1] = pk2(qv[g][2], qv[g][3]);
+    }
 
     uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
     const int n_tok = seg.t_end - seg.t_begin;
@@ -219,7 +265,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
                 const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
-                    if (safe.holds(ch)) k_chunk<BITS, G, EXACT, false, false>(w, fc, ch, qv, red, lane, 8, a.smin, a.smax);
+                    if (safe.holds(ch)) k_chunk2<BITS, G, EXACT>(w, fc, ch, pc, qv2, red, lane);
                     else k_chunk<BITS, G, EXACT, false, true>(w, fc, ch, qv, red, lane, 8, a.smin, a.smax);
                     reduce8<G>(red, lane, sum);
 #pragma unroll
@@ -286,8 +332,8 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
 
 template <int BITS, int G, bool EXACT, bool PARTIAL, bool GUARDED>
 __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
-                                        const float *wts /* [G][32] smem */, int tok0, float (&acc)[G][4],
-                                        int count, float smin, float smax)
+                                        const float2 *wts /* [G][32] smem, each weight twice */, int tok0,
+                                        float (&acc)[G][4], int count, float smin, float smax)
 {
     uint32_t grp[4] = {w.x, w.y, w.z, w.w};
     // one query head: both halves unrolled (measured faster); several heads: one body, two trips
@@ -296,8 +342,8 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> 
         float wt[G][4];
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const float4 a = *reinterpret_cast<const float4 *>(wts + g * kTileTok + tok0 + 4 * half);
-            wt[g][0] = a.x; wt[g][1] = a.y; wt[g][2] = a.z; wt[g][3] = a.w;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) wt[g][k] = wts[g * kTileTok + tok0 + 4 * half + k].x;
         }
         static_for<4>([&](auto kc) {
             constexpr int k = decltype(kc)::value;
@@ -313,6 +359,55 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> 
         });
 #pragma unroll
         for (int c = 0; c < 4; ++c) grp[c] >>= 4 * BITS;
+    }
+}
+
+// The unguarded, full 8-token case of v_chunk on channel pairs (packed fp32).  `wts2` holds every weight
+// twice ([G][32] float2) so that one 8-byte load yields the packed multiplier.
+template <int BITS, int G, bool EXACT>
+__device__ __forceinline__ void v_chunk2(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
+                                         const PairConst (&pc)[2], const float2 *wts2, int tok0, float (&acc)[G][4])
+{
+    uint32_t grp[4] = {w.x, w.y, w.z, w.w};
+    f32x2 zp[2] = {pk2(ch[0].zp, ch[1].zp), pk2(ch[2].zp, ch[3].zp)};
+    f32x2 s[2] = {pk2(ch[0].s, ch[1].s), pk2(ch[2].s, ch[3].s)};
+    const f32x2 one = opaque_ones2();
+    f32x2 acc2[G][2];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        acc2[g][0] = pk2(acc[g][0], acc[g][1]);
+        acc2[g][1] = pk2(acc[g][2], acc[g][3]);
+    }
+#pragma unroll(G == 1 ? 2 : 1)
+    for (int half = 0; half < 2; ++half) {
+        f32x2 wt[G][4];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const ulonglong2 a = *reinterpret_cast<const ulonglong2 *>(wts2 + g * kTileTok + tok0 + 4 * half);
+            const ulonglong2 b = *reinterpret_cast<const ulonglong2 *>(wts2 + g * kTileTok + tok0 + 4 * half + 2);
+            wt[g][0] = a.x; wt[g][1] = a.y; wt[g][2] = b.x; wt[g][3] = b.y;
+        }
+        static_for<4>([&](auto kc) {
+            constexpr int k = decltype(kc)::value;
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const f32x2 q2 = fc.template code2<k>(grp[2 * p], grp[2 * p + 1]);
+                const f32x2 xh = replay_step2<EXACT>(q2, zp[p], s[p], pc[p], one);
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc2[g][p] = fma2(wt[g][k], xh, acc2[g][p]);
+            }
+        });
+#pragma unroll
+        for (int c = 0; c < 4; ++c) grp[c] >>= 4 * BITS;
+    }
+    upk2(zp[0], ch[0].zp, ch[1].zp);
+    upk2(zp[1], ch[2].zp, ch[3].zp);
+    upk2(s[0], ch[0].s, ch[1].s);
+    upk2(s[1], ch[2].s, ch[3].s);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        upk2(acc2[g][0], acc[g][0], acc[g][1]);
+        upk2(acc2[g][1], acc[g][2], acc[g][3]);
     }
 }
 
@@ -333,7 +428,7 @@ struct VArgs {
 //   void store(const VArgs&, int b, int h, int lane, const float (&acc)[G][4])   write the result
 template <int BITS, int G, bool EXACT, class Src>
 __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
-                                       uint64_t *ring_bar, const float *wts, Src &src)
+                                       uint64_t *ring_bar, const float2 *wts, Src &src)
 {
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
@@ -343,6 +438,8 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
     fc.init();
     load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
     load_init_state(ch, seg.init, lane);
+    PairConst pc[2];
+    make_pair_consts<EXACT>(ch, pc);
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -370,7 +467,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     const int tok0 = wd * C::TPW + c8 * 8;
-                    if (safe.holds(ch)) v_chunk<BITS, G, EXACT, false, false>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                    if (safe.holds(ch)) v_chunk2<BITS, G, EXACT>(w, fc, ch, pc, wts, tok0, acc);
                     else v_chunk<BITS, G, EXACT, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
                     if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }

@@ -62,10 +62,27 @@ __device__ __forceinline__ uint32_t opaque_u32(uint32_t v)
 template <int BITS>
 struct FieldConsts {
     uint32_t e[4];
+    uint32_t negc[4];   // bit pattern of -(2^(23-p) + BIAS), kept in a register to build packed operands
     __device__ __forceinline__ void init()
     {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) e[k] = opaque_u32(uint32_t(127 + 23 - BITS * k) << 23);
+        for (int k = 0; k < 4; ++k) {
+            e[k] = opaque_u32(uint32_t(127 + 23 - BITS * k) << 23);
+            negc[k] = opaque_u32(__float_as_uint(-(float(1u << (23 - BITS * k)) + float(Codec<BITS>::BIAS))));
+        }
+    }
+    // codes of field K of two words as a packed pair
+    template <int K>
+    __device__ __forceinline__ unsigned long long code2(uint32_t ga, uint32_t gb) const
+    {
+        uint32_t a, b;
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(a) : "r"(ga), "n"(Codec<BITS>::FIELD << (BITS * K)), "r"(e[K]));
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(b) : "r"(gb), "n"(Codec<BITS>::FIELD << (BITS * K)), "r"(e[K]));
+        unsigned long long f, c, r;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(f) : "r"(a), "r"(b));
+        asm("mov.b64 %0, {%1, %1};" : "=l"(c) : "r"(negc[K]));
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(f), "l"(c));
+        return r;
     }
     template <int K>
     __device__ __forceinline__ float code(uint32_t group) const
@@ -111,6 +128,98 @@ __device__ __forceinline__ float replay_step(float q, Chan &c, float smin, float
         s_new = c.s * fmaf(c.beta, fabsf(q), c.tc);
     }
     c.s = GUARDED ? fminf(fmaxf(s_new, smin), smax) : s_new;
+    return xh;
+}
+
+// ------------------------------------------------------------------------------------------
+// Packed fp32 pairs.  sm_100 executes add/mul/fma.rn.f32x2 at the same FP32 rate as the scalar forms
+// but in half the issue slots; the replay is bound by issue slots, so the unguarded body works on
+// channel pairs.  Each element is rounded exactly like the scalar instruction (".rn", no flush).
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pk2(float lo, float hi)
+{
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b)
+{
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b)
+{
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c)
+{
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// a + b for a packed product `a`, as fma(a, 1, b): bit-identical to add.rn (a * 1 is exact), but not
+// something the assembler can merge with the multiply that produced `a`.  ptxas contracts
+// mul.rn.f32x2 + add.rn.f32x2 into FFMA2 when the product has no other use -- explicit ".rn", asm
+// volatile and -fmad=false do not stop it (seen in the opcode counters and as few-ulp drift of the
+// replayed state) -- and that would break the canonical, separately rounded order.  `one` must be
+// a value the assembler cannot see through (PairOnes).
+__device__ __forceinline__ f32x2 add_product2(f32x2 a, f32x2 one, f32x2 b) { return fma2(a, one, b); }
+
+__device__ __forceinline__ f32x2 abs2(f32x2 v)
+{
+    float lo, hi;
+    upk2(v, lo, hi);
+    return pk2(fabsf(lo), fabsf(hi));
+}
+
+// Per-pair constants of the recurrence.  tc = -target (canonical) or 1 - beta*target (contracted).
+struct PairConst {
+    f32x2 alpha, beta, tc;
+};
+
+// (1.0f, 1.0f) read from constant memory at run time: the assembler propagates immediates even out of
+// volatile asm, but it cannot assume the contents of a __constant__ variable.
+static __constant__ float c_one = 1.0f;
+__device__ __forceinline__ f32x2 opaque_ones2()
+{
+    const float v = *const_cast<const volatile float *>(&c_one);
+    return pk2(v, v);
+}
+
+template <bool EXACT>
+__device__ __forceinline__ void make_pair_consts(const Chan (&ch)[4], PairConst (&pc)[2])
+{
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        pc[p].alpha = pk2(ch[2 * p].alpha, ch[2 * p + 1].alpha);
+        pc[p].beta = pk2(ch[2 * p].beta, ch[2 * p + 1].beta);
+        pc[p].tc = EXACT ? pk2(-ch[2 * p].tc, -ch[2 * p + 1].tc) : pk2(ch[2 * p].tc, ch[2 * p + 1].tc);
+    }
+}
+
+// Unguarded decoder step on a channel pair: same operations, same order, same roundings as
+// replay_step<EXACT, false> on each element.
+template <bool EXACT>
+__device__ __forceinline__ f32x2 replay_step2(f32x2 q2, f32x2 &zp, f32x2 &s, const PairConst &c, f32x2 one)
+{
+    const f32x2 rh = mul2(q2, s);
+    const f32x2 xh = add_product2(rh, one, zp);
+    const f32x2 aq = abs2(q2);
+    if (EXACT) {
+        zp = add_product2(mul2(c.alpha, rh), one, zp);
+        s = add_product2(mul2(mul2(s, c.beta), add2(aq, c.tc)), one, s);
+    } else {
+        zp = fma2(c.alpha, rh, zp);
+        s = mul2(s, fma2(c.beta, aq, c.tc));
+    }
     return xh;
 }
 

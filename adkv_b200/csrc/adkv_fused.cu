@@ -16,7 +16,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
     __shared__ alignas(128) uint8_t kbuf[kStages * Tile<BITS>::BYTES];
     __shared__ alignas(128) uint8_t vbuf[kStages * Tile<BITS>::BYTES];
     __shared__ alignas(16) float red[G * 8 * 36];
-    __shared__ alignas(16) float wts[G * kTileTok];
+    __shared__ alignas(16) float2 wts[G * kTileTok];
     __shared__ FusedShared<G> fs;
     __shared__ uint64_t kbar[kStages], vbar[kStages];
 

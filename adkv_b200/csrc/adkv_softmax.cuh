@@ -36,7 +36,7 @@ struct RingSink {
 template <int G>
 struct SoftmaxSrc {
     FusedShared<G> *sh;
-    float *wts;            // [G][32]
+    float2 *wts;           // [G][32], every weight stored twice (packed multiplier for a channel pair)
     const float *mask;     // row of this batch or nullptr
     float scale2;          // scaling * log2(e)
     int n_tiles;           // tiles of this segment
@@ -74,7 +74,8 @@ struct SoftmaxSrc {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             const float v = lane < ntok ? fmaf(x[g], scale2, mk) : -INFINITY;
-            wts[g * kTileTok + lane] = update(g, v, acc);
+            const float pw = update(g, v, acc);
+            wts[g * kTileTok + lane] = make_float2(pw, pw);
         }
         __syncwarp();
         return true;

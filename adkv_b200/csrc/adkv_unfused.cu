@@ -53,12 +53,15 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs k
 template <int G>
 struct GlobalWeightSrc {
     const __half *row[G];   // attention weights of each q head of this stream: [T+1]
-    float *wts;
+    float2 *wts;   // every weight stored twice
     __device__ __forceinline__ bool tile_weights(int i, int ntok, int lane, float (&)[G][4])
     {
 #pragma unroll
         for (int g = 0; g < G; ++g)
-            wts[g * kTileTok + lane] = lane < ntok ? __half2float(row[g][i * kTileTok + lane]) : 0.f;
+        {
+            const float wv = lane < ntok ? __half2float(row[g][i * kTileTok + lane]) : 0.f;
+            wts[g * kTileTok + lane] = make_float2(wv, wv);
+        }
         __syncwarp();
         return true;
     }
@@ -80,7 +83,7 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_ov_kernel(VArgs v
                                                                          int n_streams)
 {
     __shared__ alignas(128) uint8_t vbuf[kStreamsPerCta][kStages * Tile<BITS>::BYTES];
-    __shared__ alignas(16) float wts[kStreamsPerCta][G * kTileTok];
+    __shared__ alignas(16) float2 wts[kStreamsPerCta][G * kTileTok];
     __shared__ uint64_t vbar[kStreamsPerCta][kStages];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) {
