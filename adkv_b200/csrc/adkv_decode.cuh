@@ -122,12 +122,12 @@ __device__ __forceinline__ void k_chunk(const uint4 &w, const FieldConsts<BITS> 
 // state; the per-lane partial dot product is summed in a different order (pairs first).
 template <int BITS, int G, bool EXACT>
 __device__ __forceinline__ void k_chunk2(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
-                                         const PairConst (&pc)[2], const f32x2 (&qv2)[G][2], float *red, int lane)
+                                         const PairConst (&pc)[2], f32x2 one, const f32x2 (&qv2)[G][2], float *red,
+                                         int lane)
 {
     uint32_t grp[4] = {w.x, w.y, w.z, w.w};
     f32x2 zp[2] = {pk2(ch[0].zp, ch[1].zp), pk2(ch[2].zp, ch[3].zp)};
     f32x2 s[2] = {pk2(ch[0].s, ch[1].s), pk2(ch[2].s, ch[3].s)};
-    const f32x2 one = opaque_ones2();
 #pragma unroll(G == 1 ? 2 : 1)
     for (int half = 0; half < 2; ++half) {
         static_for<4>([&](auto kc) {
@@ -235,6 +235,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
     for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane);
     PairConst pc[2];
     make_pair_consts<EXACT>(ch, pc);
+    const f32x2 one = opaque_ones2();   // read once: a constant-memory load per chunk would stall the chain
     f32x2 qv2[G][2];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -265,7 +266,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
                 const uint4 w_next = tile[min(wd + 1, Tile<BITS>::WORDS - 1) * (kD / 4)];
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
-                    if (safe.holds(ch)) k_chunk2<BITS, G, EXACT>(w, fc, ch, pc, qv2, red, lane);
+                    if (safe.holds(ch)) k_chunk2<BITS, G, EXACT>(w, fc, ch, pc, one, qv2, red, lane);
                     else k_chunk<BITS, G, EXACT, false, true>(w, fc, ch, qv, red, lane, 8, a.smin, a.smax);
                     reduce8<G>(red, lane, sum);
 #pragma unroll
@@ -366,12 +367,12 @@ __device__ __forceinline__ void v_chunk(const uint4 &w, const FieldConsts<BITS> 
 // twice ([G][32] float2) so that one 8-byte load yields the packed multiplier.
 template <int BITS, int G, bool EXACT>
 __device__ __forceinline__ void v_chunk2(const uint4 &w, const FieldConsts<BITS> &fc, Chan (&ch)[4],
-                                         const PairConst (&pc)[2], const float2 *wts2, int tok0, float (&acc)[G][4])
+                                         const PairConst (&pc)[2], f32x2 one, const float2 *wts2, int tok0,
+                                         float (&acc)[G][4])
 {
     uint32_t grp[4] = {w.x, w.y, w.z, w.w};
     f32x2 zp[2] = {pk2(ch[0].zp, ch[1].zp), pk2(ch[2].zp, ch[3].zp)};
     f32x2 s[2] = {pk2(ch[0].s, ch[1].s), pk2(ch[2].s, ch[3].s)};
-    const f32x2 one = opaque_ones2();
     f32x2 acc2[G][2];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -440,6 +441,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
     load_init_state(ch, seg.init, lane);
     PairConst pc[2];
     make_pair_consts<EXACT>(ch, pc);
+    const f32x2 one = opaque_ones2();   // read once: a constant-memory load per chunk would stall the chain
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -467,7 +469,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     const int tok0 = wd * C::TPW + c8 * 8;
-                    if (safe.holds(ch)) v_chunk2<BITS, G, EXACT>(w, fc, ch, pc, wts, tok0, acc);
+                    if (safe.holds(ch)) v_chunk2<BITS, G, EXACT>(w, fc, ch, pc, one, wts, tok0, acc);
                     else v_chunk<BITS, G, EXACT, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
                     if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }

@@ -46,6 +46,7 @@ WORKLOADS = {
     "profile_prefill_b16_t2048_2bit": dict(kind="encode", B=16, Hq=32, Hkv=32, D=128, T=2048, bits=2, appends=8),
     # profiling-sized cases: same kernels and per-stream work, a few hundred MB on the device
     "profile_b16_t4096_4bit": dict(B=16, Hq=32, Hkv=32, D=128, T=4096, bits=4),
+    "profile_b64_t4096_4bit": dict(B=64, Hq=32, Hkv=32, D=128, T=4096, bits=4),
     "profile_gqa_b8_t16384_2bit": dict(B=8, Hq=32, Hkv=8, D=128, T=16384, bits=2),
 }
 DEFAULT_WORKLOAD = "config2_llama2_7b_b128_t4096_4bit"
