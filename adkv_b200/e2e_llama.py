@@ -1,0 +1,270 @@
+"""End-to-end decode harness: a random-init Llama-architecture decoder on top of the ADKV kernels.
+
+This is the caller side of the hot path for the end-to-end configuration (32 layers, d_model 4096,
+32 heads, FFN 11008, fp16 weights ~ N(0, 0.02), random-token prompt, greedy generation with a 4-bit
+ADKV cache), in the role of the reference's ``src/adkv/hf/llama_adkv.py`` + ``tools/perf_e2e.py``:
+prefill runs dense causal attention on the prompt and quantises K/V into the packed caches
+(``llama_adkv.py:358-378``), every decode step attends over the packed cache and appends the new
+token (``llama_adkv.py:347-355``).  Differences that make it a B200 serving loop rather than a
+port: caches are sized once for prompt + generation; one fused ``decode_attn`` launch per layer
+replaces qk -> softmax -> ov; K and V of a layer are quantised in one launch; and the model can be
+tensor-parallel over the GPUs of a node (heads and FFN columns sharded, two NCCL all-reduces per
+layer on the ``[B, d_model]`` activations, which are the only NVLink traffic -- attention itself
+never leaves its GPU).
+
+Everything except attention and quantisation is plain torch (cuBLAS GEMMs): it is plumbing around
+the kernels, not part of what is measured against the roofline.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import gemv, synth
+
+
+@dataclass
+class LlamaShape:
+    n_layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    vocab: int = 32000
+    rope_theta: float = 10000.0
+    norm_eps: float = 1e-5
+
+
+def _rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def _rope_tables(shape: LlamaShape, max_pos: int, device):
+    half = shape.head_dim // 2
+    inv = shape.rope_theta ** (-torch.arange(0, half, device=device, dtype=torch.float32) * 2.0 / shape.head_dim)
+    ang = torch.arange(max_pos, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)     # [P, D] fp32
+
+
+def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B, H, T, D]; cos/sin [T, D] (HF rotate_half convention)."""
+    half = x.shape[-1] // 2
+    xf = x.float()
+    rot = torch.cat([-xf[..., half:], xf[..., :half]], -1)
+    return (xf * cos + rot * sin).to(x.dtype)
+
+
+class ADKVLlama:
+    """One tensor-parallel shard of the model with its packed KV caches."""
+
+    def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, bits: int = 4, device="cuda",
+                 rank: int = 0, world: int = 1, seed: int = 0, fused: bool = True, fast: bool = False,
+                 ckpt_interval: int = 0):
+        assert shape.n_heads % world == 0 and shape.n_kv_heads % world == 0 and shape.ffn % world == 0
+        self.s, self.B, self.bits, self.dev = shape, batch, bits, torch.device(device)
+        self.rank, self.world, self.fused, self.fast, self.ckpt_interval = rank, world, fused, fast, ckpt_interval
+        self.hq, self.hkv, self.ffn = shape.n_heads // world, shape.n_kv_heads // world, shape.ffn // world
+        D, dm = shape.head_dim, shape.d_model
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(seed)                       # same seed on every rank: replicated tensors agree
+
+        def rnd(*sz):
+            return (torch.randn(*sz, generator=g, device=self.dev, dtype=torch.float32) * 0.02).half()
+
+        self.embed = rnd(shape.vocab, dm)
+        self.lm_head = rnd(shape.vocab, dm)
+        self.final_norm = torch.ones(dm, dtype=torch.float16, device=self.dev)
+        self.layers = []
+        h0, k0, f0 = rank * self.hq, rank * self.hkv, rank * self.ffn
+        for li in range(shape.n_layers):
+            # every rank draws the full-size layer from the same seed and keeps its slice, so the model is the
+            # same function whatever the tensor-parallel degree
+            gl = torch.Generator(device=self.dev)
+            gl.manual_seed(seed * 1000 + li + 1)
+
+            def rl(*sz):
+                return (torch.randn(*sz, generator=gl, device=self.dev, dtype=torch.float32) * 0.02).half()
+
+            wq, wk, wv = rl(shape.n_heads * D, dm), rl(shape.n_kv_heads * D, dm), rl(shape.n_kv_heads * D, dm)
+            wo, wg, wu, wd = rl(dm, shape.n_heads * D), rl(shape.ffn, dm), rl(shape.ffn, dm), rl(dm, shape.ffn)
+            kp = synth.gen_params(seed + 7 * li + 1, shape.n_kv_heads, D, bits, device=self.dev)
+            vp = synth.gen_params(seed + 7 * li + 2, shape.n_kv_heads, D, bits, device=self.dev)
+            self.layers.append(dict(
+                wqkv=torch.cat([wq[h0 * D:(h0 + self.hq) * D], wk[k0 * D:(k0 + self.hkv) * D],
+                                wv[k0 * D:(k0 + self.hkv) * D]]).contiguous(),
+                wo=wo[:, h0 * D:(h0 + self.hq) * D].contiguous(),
+                w_gate_up=torch.cat([wg[f0:f0 + self.ffn], wu[f0:f0 + self.ffn]]).contiguous(),
+                w_down=wd[:, f0:f0 + self.ffn].contiguous(),
+                norm1=torch.ones(dm, dtype=torch.float16, device=self.dev),
+                norm2=torch.ones(dm, dtype=torch.float16, device=self.dev),
+                kp=tuple(p[k0:k0 + self.hkv].contiguous() for p in kp),
+                vp=tuple(p[k0:k0 + self.hkv].contiguous() for p in vp)))
+            del wq, wk, wv, wo, wg, wu, wd
+        ns = gemv.n_super_for(max_tokens, bits)
+        for L in self.layers:
+            L["kc"] = torch.zeros((batch, self.hkv, ns, D // 4, 4, 4), dtype=torch.uint8, device=self.dev)
+            L["vc"] = torch.zeros_like(L["kc"])
+            if ckpt_interval:
+                L["kck"] = gemv.alloc_ckpt(batch, self.hkv, D, max_tokens, ckpt_interval, self.dev)
+                L["vck"] = gemv.alloc_ckpt(batch, self.hkv, D, max_tokens, ckpt_interval, self.dev)
+        self.cos, self.sin = _rope_tables(shape, max_tokens, self.dev)
+        self.T = 0
+        self.scaling = D ** -0.5
+        self.scratch = None
+        if ckpt_interval:
+            self.scratch = torch.empty(gemv.decode_scratch_bytes(batch, self.hq, self.hkv, max_tokens, ckpt_interval),
+                                       dtype=torch.uint8, device=self.dev)
+
+    # ------------------------------------------------------------------ helpers
+    def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(x)
+        return x
+
+    def _mlp(self, L, x):
+        gu = x @ L["w_gate_up"].T
+        gate, up = gu[..., :self.ffn], gu[..., self.ffn:]
+        return self._allreduce((F.silu(gate) * up) @ L["w_down"].T)
+
+    def _qkv(self, L, h, T_new):
+        B = h.shape[0]
+        D = self.s.head_dim
+        qkv = (h @ L["wqkv"].T).view(B, T_new, self.hq + 2 * self.hkv, D).transpose(1, 2)     # [B, H*, T, D]
+        return qkv[:, :self.hq], qkv[:, self.hq:self.hq + self.hkv], qkv[:, self.hq + self.hkv:]
+
+    def _ck(self, L):
+        return dict(k_ckpt=L["kck"], v_ckpt=L["vck"], ckpt_interval=self.ckpt_interval) if self.ckpt_interval else {}
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, batch_chunk: int = 16) -> torch.Tensor:
+        """ids [B, Tp] -> next-token ids [B]; fills the caches with the quantised prompt."""
+        B, Tp = ids.shape
+        assert B == self.B and self.T == 0
+        cos, sin = self.cos[:Tp], self.sin[:Tp]
+        nxt = []
+        for b0 in range(0, B, batch_chunk):
+            b1 = min(B, b0 + batch_chunk)
+            x = self.embed[ids[b0:b1]]
+            for L in self.layers:
+                h = _rms_norm(x, L["norm1"], self.s.norm_eps)
+                q, k, v = self._qkv(L, h, Tp)
+                q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
+                gemv.encode_kv_pair(L["kc"][b0:b1], k.contiguous(), L["kp"], L["vc"][b0:b1], v.contiguous(), L["vp"],
+                                    synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits,
+                                    **({"k_ckpt": L["kck"][b0:b1], "v_ckpt": L["vck"][b0:b1],
+                                        "ckpt_interval": self.ckpt_interval} if self.ckpt_interval else {}))
+                att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.hq != self.hkv)
+                x = x + self._allreduce(att.transpose(1, 2).reshape(b1 - b0, Tp, -1) @ L["wo"].T)
+                x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
+            last = _rms_norm(x[:, -1], self.final_norm, self.s.norm_eps)
+            nxt.append((last @ self.lm_head.T).argmax(-1))
+        self.T = Tp
+        return torch.cat(nxt)
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [B] (the tokens at position T) -> next-token ids [B]; appends position T to the caches."""
+        T = self.T
+        cos, sin = self.cos[T:T + 1], self.sin[T:T + 1]
+        x = self.embed[ids][:, None, :]                                                  # [B, 1, dm]
+        for L in self.layers:
+            h = _rms_norm(x, L["norm1"], self.s.norm_eps)
+            q, k, v = self._qkv(L, h, 1)
+            q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
+            v = v.contiguous()
+            if self.fused:
+                att = gemv.decode_attn(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], T, self.scaling,
+                                       synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, fast=self.fast,
+                                       scratch=self.scratch, **self._ck(L))
+            else:   # the reference caller's three-call sequence (llama_adkv.py:263-276)
+                logits = gemv.forward_qk(q, L["kc"], k, *L["kp"], T, synth.SCALE_MIN, synth.SCALE_MAX,
+                                         bits=self.bits, fast=self.fast)
+                w = torch.softmax(logits.float() * self.scaling, dim=-1).to(torch.float16)
+                att = gemv.forward_ov(w, L["vc"], v, *L["vp"], synth.SCALE_MIN, synth.SCALE_MAX,
+                                      bits=self.bits, fast=self.fast)
+            x = x + self._allreduce(att.reshape(self.B, 1, -1) @ L["wo"].T)
+            x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
+        self.T = T + 1
+        last = _rms_norm(x[:, 0], self.final_norm, self.s.norm_eps)
+        return (last @ self.lm_head.T).argmax(-1)
+
+
+def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fused: bool = True, fast: bool = False,
+        ckpt_interval: int = 0, seed: int = 0) -> dict:
+    """Prefill a random prompt, generate `gen` tokens greedily; timings with CUDA events, max over ranks."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    model = ADKVLlama(shape, batch, prompt + gen, bits=bits, device=dev, rank=rank, world=world, seed=seed,
+                      fused=fused, fast=fast, ckpt_interval=ckpt_interval)
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed + 99)
+    ids = torch.randint(0, shape.vocab, (batch, prompt), generator=g, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    ev[0].record()
+    tok = model.prefill(ids)
+    ev[1].record()
+    out = [tok]
+    for _ in range(gen):
+        tok = model.decode(tok)
+        out.append(tok)
+    ev[2].record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms = t.tolist()
+    status = gemv.device_status(dev)
+    toks = torch.stack(out, 1)
+    return dict(rank=rank, world=world, prefill_ms=prefill_ms, decode_ms=decode_ms,
+                decode_tokens_per_s=batch * gen / (decode_ms * 1e-3), ms_per_decode_step=decode_ms / gen,
+                prefill_tokens_per_s=batch * prompt / (prefill_ms * 1e-3), device_status=status,
+                token_checksum=int(toks.sum().item()), tokens=toks)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--gen", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--unfused", action="store_true")
+    ap.add_argument("--fast", action="store_true")
+    ap.add_argument("--ckpt-interval", type=int, default=0)
+    a = ap.parse_args()
+    shape = LlamaShape(n_layers=a.layers)
+    r = run(shape, a.batch, a.prompt, a.gen, bits=a.bits, fused=not a.unfused, fast=a.fast,
+            ckpt_interval=a.ckpt_interval)
+    if r["rank"] == 0:
+        r.pop("tokens")
+        r.update(metric="e2e_decode_tokens_per_s", config=dict(model="random-init Llama-2-7B architecture", batch=a.batch,
+                 prompt=a.prompt, generate=a.gen, layers=a.layers, bits=a.bits, fused=not a.unfused,
+                 replay="fast" if a.fast else "exact", tensor_parallel=r["world"], data="synthetic"))
+        print(json.dumps(r), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,42 @@
+"""The end-to-end decode harness on a tiny random-init model: plumbing around the kernels (RoPE position,
+cache indexing, fused vs the reference caller's three-call sequence, checkpointed decode)."""
+import pytest
+import torch
+
+from adkv_b200.e2e_llama import ADKVLlama, LlamaShape
+
+pytestmark = pytest.mark.gpu
+
+TINY = LlamaShape(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=503)
+
+
+def _generate(prompt_ids, gen, **kw):
+    m = ADKVLlama(TINY, prompt_ids.shape[0], prompt_ids.shape[1] + gen, device="cuda", seed=3, **kw)
+    tok = m.prefill(prompt_ids)
+    toks = [tok]
+    for _ in range(gen):
+        tok = m.decode(tok)
+        toks.append(tok)
+    assert m.T == prompt_ids.shape[1] + gen
+    return torch.stack(toks, 1), m
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_generation_paths_agree(bits):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ids = torch.randint(0, TINY.vocab, (3, 37), generator=g, device="cuda")
+    a, ma = _generate(ids, 30, bits=bits, fused=True)
+    b, mb = _generate(ids, 30, bits=bits, fused=True)
+    assert torch.equal(a, b)                                          # deterministic
+    c, mc = _generate(ids, 30, bits=bits, fused=True, ckpt_interval=32)
+    d, md = _generate(ids, 30, bits=bits, fused=False)                # qk -> torch softmax -> ov
+    # Greedy decoding can diverge after a near-tie between two logits (the three paths sum in different
+    # orders, and the three-call path rounds logits and weights to fp16): require agreement on most
+    # positions, and identical prompt codes.
+    for other, mo in ((c, mc), (d, md)):
+        agree = (a == other).float().mean().item()
+        assert agree > 0.8, agree
+        n_prompt_words = 37 // (32 // bits)
+        for La, Lo in zip(ma.layers, mo.layers):
+            assert torch.equal(La["kc"][:, :, :n_prompt_words], Lo["kc"][:, :, :n_prompt_words])
+            assert torch.equal(La["vc"][:, :, :n_prompt_words], Lo["vc"][:, :, :n_prompt_words])
