@@ -53,13 +53,13 @@ DEFAULT_WORKLOAD = "config2_llama2_7b_b128_t4096_4bit"
 METRIC = "fused_adkv_decode_attn_packed_kv_bandwidth"
 UNIT = "GB/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
-# summarised under profiles/ (bytes); None where no capture exists for the workload.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel (bytes), from an ncu capture;
+# None where no capture exists for the workload.
 NCU_TRAFFIC_BYTES = {
-    # 273.1 MB measured on the batch-16 capture (profiles/decode_attn_kernel_4bit_b16_t4096.md); streams are
-    # independent, so traffic scales with the batch: x8 for batch 128
-    "config2_llama2_7b_b128_t4096_4bit": 8 * 273_142_784,
-    "profile_b16_t4096_4bit": 273_142_784,
+    # 273.3 MB measured on a batch-16 capture of the same kernel; streams are independent, so traffic scales
+    # with the batch: x8 for batch 128
+    "config2_llama2_7b_b128_t4096_4bit": 8 * 273_308_672,
+    "profile_b16_t4096_4bit": 273_308_672,
 }
 
 

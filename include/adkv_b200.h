@@ -20,7 +20,7 @@
  * Arithmetic: the fp32 recurrence of src/adkv/train/train_model.py:6-22, 70-81 (the
  * reference's torch/Triton definition), evaluated with one rounding per operation in that
  * order ("canonical").  ADKV_FLAG_FAST_REPLAY lets the decode kernels replay the cached
- * tokens with fused multiply-adds instead (see DESIGN notes in the repository): attention
+ * tokens with fused multiply-adds instead (zp = fma(alpha, q*s, zp), s = clamp(s * fma(beta, |q|, 1 - beta*target))): attention
  * outputs stay within tolerance, and an appended code may differ from the canonical one by
  * one step in rare cases.
  */

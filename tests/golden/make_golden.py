@@ -76,7 +76,9 @@ def run_case(tm, recorded, x16, params, bits, smin, smax):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     tm, recorded = load_reference(ref_root)
     from adkv_b200 import synth
 

@@ -255,7 +255,7 @@ def test_unfused_trio_matches_fused():
 
 
 def test_full_size_config2_properties():
-    """BASELINE config 2 shape (B 128, H 32, T 4096, 4-bit): the batch is 2 distinct sequences replicated 64
+    """The headline benchmark shape (B 128, H 32, T 4096, 4-bit): the batch is 2 distinct sequences replicated 64
     times, so every replica must reproduce the oracle's result for its sequence, and the appended slot must
     equal the oracle's.  Also checks that re-running the step with the same T overwrites the same slot."""
     B, H, T, bits, D, R = 128, 32, 4096, 4, 128, 2
@@ -293,7 +293,7 @@ def test_full_size_config2_properties():
 
 
 def test_full_size_config5_gqa_2bit_properties():
-    """BASELINE config 5 shape (B 32, 32 q heads over 8 KV heads, T 32768, 2-bit): one distinct sequence
+    """The long-context GQA benchmark shape (B 32, 32 q heads over 8 KV heads, T 32768, 2-bit): one distinct sequence
     replicated over the batch; every replica must reproduce the oracle's result and appended codes."""
     B, Hq, Hkv, T, bits, D = 32, 32, 8, 32768, 2, 128
     from oracle import c_oracle
@@ -325,7 +325,7 @@ def test_full_size_config5_gqa_2bit_properties():
 
 @pytest.mark.parametrize("bits", [4, 2])
 def test_full_size_config3_prefill_properties(bits):
-    """BASELINE config 3 shape for one layer (B 16, H 32, T 8192): 2 distinct sequences replicated; every
+    """The prefill-quantise benchmark shape for one layer (B 16, H 32, T 8192): 2 distinct sequences replicated; every
     replica equals the oracle's codes and tail state; encoding in three chunks and appending the last 256
     tokens one by one gives the same cache as the one-shot prefill."""
     B, H, T, D, R, A = 16, 32, 8192, 128, 2, 256
