@@ -27,8 +27,10 @@ constexpr int kD = 128;              // head dim served by this build
 constexpr float kEps = 1e-8f;        // src/adkv/train/train_model.py:9
 constexpr unsigned kFull = 0xffffffffu;
 
-// Status codes written to g_status when a bounded wait gives up.
+// Status codes written to g_status when a bounded wait gives up (1-5) or an argument only the device can
+// see is unusable (6).
 constexpr int kStatKWait = 1, kStatVWait = 2, kStatLFullWait = 3, kStatLEmptyWait = 4, kStatDrain = 5;
+constexpr int kStatCapacity = 6;   // a device-side sequence length did not fit the cache: that stream was skipped
 
 // One status word per translation unit that includes this header (the library is one unit).
 static __device__ int g_status = 0;

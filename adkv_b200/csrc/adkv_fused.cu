@@ -11,7 +11,8 @@ namespace adkv {
 
 template <int BITS, int G, bool EXACT>
 __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
-                                                         long long mask_stride_b, float scaling)
+                                                         long long mask_stride_b, float scaling,
+                                                         const int *__restrict__ seq_lens)
 {
     __shared__ alignas(128) uint8_t kbuf[kStages * Tile<BITS>::BYTES];
     __shared__ alignas(128) uint8_t vbuf[kStages * Tile<BITS>::BYTES];
@@ -22,6 +23,17 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
 
     const int bh = blockIdx.x, b = bh / ka.Hkv, h = bh % ka.Hkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (seq_lens) {
+        // per-sequence token counts held on the device (ragged batches; also lets a captured launch be
+        // replayed while the sequences grow).  The host could not check the capacity, so it is checked here.
+        const int T = seq_lens[b];
+        if (T < 0 || T / Codec<BITS>::TPW >= ka.n_super_cap) {
+            if (threadIdx.x == 0) atomicExch(&g_status, kStatCapacity);
+            return;
+        }
+        ka.T = T;
+        va.T = T;
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mbar_init(&kbar[i], 1); mbar_init(&vbar[i], 1); }
         for (int i = 0; i < kLogitSlots; ++i) { mbar_init(&fs.lfull[i], 1); mbar_init(&fs.lempty[i], 1); }
@@ -81,7 +93,31 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(
-                      ka, va, static_cast<const float *>(mask), mask_stride_b, scaling)))
+                      ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, nullptr)))
+    return launch_status();
+}
+
+int adkv_decode_attn_varlen(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                            const adkv_params *kp, const adkv_params *vp, const void *seq_lens, void *out, int B,
+                            int Hq, int Hkv, int D, int n_super_cap, int bits, float scaling, float scale_min,
+                            float scale_max, unsigned flags, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !seq_lens || !params_ok(kp) || !params_ok(vp))
+        return ADKV_E_NULL;
+    if (int rc = check_common(B, Hq, Hkv, 0, D, n_super_cap, bits, 1)) return rc;
+    if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
+        !aligned8(v_new) || !params_aligned(kp) || !params_aligned(vp) || (reinterpret_cast<uintptr_t>(seq_lens) & 3u))
+        return ADKV_E_ALIGN;
+    if (B == 0) return 0;
+    const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max};
+    const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
+                   to_ptrs(vp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    ADKV_DISPATCH(bits, exact, Hq / Hkv,
+                  (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(ka, va, nullptr, 0, scaling,
+                                                                            static_cast<const int *>(seq_lens))))
     return launch_status();
 }
 

@@ -172,6 +172,55 @@ class ADKVLlama:
         self.T = Tp
         return torch.cat(nxt)
 
+    # ------------------------------------------------------------------ decode, replayable
+    @torch.no_grad()
+    def _decode_body(self, ids: torch.Tensor) -> torch.Tensor:
+        """One decode step in which nothing on the host depends on the position: the token count lives in
+        ``self.seq_lens`` on the device (read by the attention kernel and the RoPE lookup, incremented at the
+        end), so the recorded sequence of launches is the same for every step."""
+        pos = self.seq_lens[:1].long()
+        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+        x = self.embed[ids][:, None, :]
+        for L in self.layers:
+            h = _rms_norm(x, L["norm1"], self.s.norm_eps)
+            q, k, v = self._qkv(L, h, 1)
+            q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
+            att = gemv.decode_attn_varlen(q, L["kc"], L["vc"], k, v.contiguous(), L["kp"], L["vp"], self.seq_lens,
+                                          self.scaling, synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits,
+                                          fast=self.fast)
+            x = x + self._allreduce(att.reshape(self.B, 1, -1) @ L["wo"].T)
+            x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
+        self.seq_lens += 1
+        last = _rms_norm(x[:, 0], self.final_norm, self.s.norm_eps)
+        return (last @ self.lm_head.T).argmax(-1)
+
+    @torch.no_grad()
+    def capture_decode(self, warmup_ids: torch.Tensor, warmup_steps: int = 3) -> torch.Tensor:
+        """Run `warmup_steps` real decode steps eagerly, then record one step into a CUDA graph.
+        Returns the token ids after the warm-up steps; continue with :meth:`decode_replay`."""
+        self.seq_lens = torch.full((self.B,), self.T, dtype=torch.int32, device=self.dev)
+        self._g_in = warmup_ids.clone()
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            tok = self._g_in
+            for _ in range(warmup_steps):
+                tok = self._decode_body(tok)
+            self._g_in.copy_(tok)
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        self.T += warmup_steps
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._g_out = self._decode_body(self._g_in)
+        return self._g_in.clone()
+
+    @torch.no_grad()
+    def decode_replay(self, ids: torch.Tensor) -> torch.Tensor:
+        self._g_in.copy_(ids)
+        self._graph.replay()
+        self.T += 1
+        return self._g_out.clone()
+
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
     def decode(self, ids: torch.Tensor) -> torch.Tensor:
@@ -202,7 +251,7 @@ class ADKVLlama:
 
 
 def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fused: bool = True, fast: bool = False,
-        ckpt_interval: int = 0, seed: int = 0) -> dict:
+        ckpt_interval: int = 0, seed: int = 0, graph: bool = False) -> dict:
     """Prefill a random prompt, generate `gen` tokens greedily; timings with CUDA events, max over ranks."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -224,9 +273,18 @@ def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fus
     tok = model.prefill(ids)
     ev[1].record()
     out = [tok]
-    for _ in range(gen):
-        tok = model.decode(tok)
+    if graph:
+        # the warm-up steps and the capture are part of the timed decode region
+        warm = min(3, gen)
+        tok = model.capture_decode(tok, warm)
         out.append(tok)
+        for _ in range(gen - warm):
+            tok = model.decode_replay(tok)
+            out.append(tok)
+    else:
+        for _ in range(gen):
+            tok = model.decode(tok)
+            out.append(tok)
     ev[2].record()
     torch.cuda.synchronize(dev)
     t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], dtype=torch.float64, device=dev)
@@ -251,15 +309,17 @@ def main():
     ap.add_argument("--unfused", action="store_true")
     ap.add_argument("--fast", action="store_true")
     ap.add_argument("--ckpt-interval", type=int, default=0)
+    ap.add_argument("--graph", action="store_true", help="replay the decode step from a CUDA graph (device-side lengths)")
     a = ap.parse_args()
     shape = LlamaShape(n_layers=a.layers)
     r = run(shape, a.batch, a.prompt, a.gen, bits=a.bits, fused=not a.unfused, fast=a.fast,
-            ckpt_interval=a.ckpt_interval)
+            ckpt_interval=a.ckpt_interval, graph=a.graph)
     if r["rank"] == 0:
         r.pop("tokens")
         r.update(metric="e2e_decode_tokens_per_s", config=dict(model="random-init Llama-2-7B architecture", batch=a.batch,
                  prompt=a.prompt, generate=a.gen, layers=a.layers, bits=a.bits, fused=not a.unfused,
-                 replay="fast" if a.fast else "exact", tensor_parallel=r["world"], data="synthetic"))
+                 replay="fast" if a.fast else "exact", tensor_parallel=r["world"], cuda_graph=a.graph,
+                 data="synthetic"))
         print(json.dumps(r), flush=True)
     if dist.is_initialized():
         dist.barrier()

@@ -25,7 +25,8 @@ import torch
 from . import _lib
 
 __all__ = ["encode_kv", "forward_qk", "forward_ov", "decode_attn", "append_kv", "encode_kv_pair",
-           "append_kv_pair", "n_super_for", "alloc_ckpt", "ckpt_capacity", "decode_scratch_bytes"]
+           "append_kv_pair", "n_super_for", "alloc_ckpt", "ckpt_capacity", "decode_scratch_bytes",
+           "decode_attn_varlen", "decode_attn_static"]
 
 
 def n_super_for(tokens: int, bits: int = 4) -> int:
@@ -342,6 +343,45 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
                                               mstride, out.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scaling,
                                               scale_min, scale_max, flags, _stream(k_cache))
     _lib.check(rc, "decode_attn")
+    return out
+
+
+def decode_attn_varlen(q, k_cache, v_cache, k_new, v_new, k_params, v_params, seq_lens, scaling: float,
+                       scale_min, scale_max, *, bits: int = 4, fast: bool = False, out: torch.Tensor | None = None):
+    """Fused decode step with per-sequence lengths on the device.
+
+    ``seq_lens`` int32 ``[B]`` CUDA tensor: sequence ``b`` attends over its ``seq_lens[b]`` cached tokens and
+    appends the new token at that position (the caller advances ``seq_lens`` afterwards, on the device).
+    Otherwise as :func:`decode_attn` without a mask.  Nothing in the call depends on the lengths' values, so
+    the same launch can be replayed step after step (e.g. from a captured CUDA graph)."""
+    _require(q.dtype == torch.float16, "q must be float16")
+    _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "k_new / v_new must be float16")
+    B, Hkv, n_super_cap, D = _cache_dims(k_cache, "k_cache")
+    _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
+             "v_cache must match k_cache")
+    _require(k_cache.is_contiguous() and v_cache.is_contiguous(), "caches must be contiguous (appended in place)")
+    _require(q.dim() == 4 and q.shape[2] == 1 and q.shape[0] == B and q.shape[3] == D, "q must be [B, nh, 1, DIM]")
+    Hq = q.shape[1]
+    _require(Hq % Hkv == 0, "q heads must be a multiple of the cache's heads")
+    _require(k_new.numel() == B * Hkv * D and v_new.numel() == B * Hkv * D, "k_new / v_new must be [B, nh, 1, DIM]")
+    _require(seq_lens.dtype == torch.int32 and seq_lens.is_cuda and seq_lens.is_contiguous() and seq_lens.numel() == B,
+             "seq_lens must be a contiguous int32 CUDA tensor with one entry per sequence")
+    names = ("zp", "sc", "alpha", "beta", "t")
+    kp, keep_k = _params(tuple("k_" + n for n in names), tuple(k_params), Hkv, D, k_cache.device)
+    vp, keep_v = _params(tuple("v_" + n for n in names), tuple(v_params), Hkv, D, k_cache.device)
+    qc, kn, vn = q.contiguous(), k_new.contiguous(), v_new.contiguous()
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.float16, device=k_cache.device)
+    else:
+        _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
+                 "out must be contiguous float16 [B, nh_q, DIM]")
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().adkv_decode_attn_varlen(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
+                                                 vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp),
+                                                 seq_lens.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, n_super_cap,
+                                                 bits, scaling, scale_min, scale_max,
+                                                 _lib.FLAG_FAST_REPLAY if fast else 0, _stream(k_cache))
+    _lib.check(rc, "decode_attn_varlen")
     return out
 
 

@@ -122,6 +122,17 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
                      void *out, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
                      float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
 
+/* adkv_decode_attn with per-sequence token counts held on the device: seq_lens int32 [B]; sequence b attends
+ * over its tokens [0, seq_lens[b]) and appends its new token at seq_lens[b].  No counterpart in the reference
+ * (one host integer T for the whole batch, src/adkv/kernel/gemv.py:25).  Serves ragged batches without padding
+ * masks, and -- because no argument changes from step to step when the caller increments seq_lens on the
+ * device -- a launch that is replayed unchanged.  A length that does not fit the cache cannot be rejected on
+ * the host: that stream is skipped and adkv_device_status reports 6. */
+int adkv_decode_attn_varlen(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
+                            const adkv_params *kp, const adkv_params *vp, const void *seq_lens, void *out,
+                            int B, int Hq, int Hkv, int D, int n_super_cap, int bits, float scaling,
+                            float scale_min, float scale_max, unsigned flags, void *stream);
+
 /* ---- State checkpoints (opt-in; no counterpart in the reference's code, proposed in its paper for long
  * contexts).  A checkpoint tensor float [B, H, n_ckpt_cap, 2, D] per cache holds, in entry k, the recurrence
  * state (zp then scale) before token (k+1)*interval; `interval` is a multiple of 32.  With them the token
@@ -174,8 +185,8 @@ int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, co
                                  float scale_min, float scale_max, unsigned flags, void *stream);
 
 /* Reads and clears the device-side status word of the current device (HOST pointer `status`;
- * synchronises `stream`).  Non-zero means a kernel gave up on a bounded wait; the value encodes
- * which wait.  Intended for tests and diagnostics, not for the hot path. */
+* synchronises `stream`).  Non-zero means a kernel gave up on a bounded wait (1-5: which wait) or skipped a
+ * stream whose device-side length did not fit the cache (6).  Intended for tests and diagnostics, not for the hot path. */
 int adkv_device_status(int *status, void *stream);
 
 #ifdef __cplusplus

@@ -40,3 +40,23 @@ def test_generation_paths_agree(bits):
         for La, Lo in zip(ma.layers, mo.layers):
             assert torch.equal(La["kc"][:, :, :n_prompt_words], Lo["kc"][:, :, :n_prompt_words])
             assert torch.equal(La["vc"][:, :, :n_prompt_words], Lo["vc"][:, :, :n_prompt_words])
+
+
+def test_graph_replay_matches_eager_steps():
+    g = torch.Generator(device="cuda").manual_seed(1)
+    ids = torch.randint(0, TINY.vocab, (2, 21), generator=g, device="cuda")
+    eager, me = _generate(ids, 20)
+    m = ADKVLlama(TINY, 2, 21 + 20, device="cuda", seed=3)
+    tok = m.prefill(ids)
+    toks = [tok]
+    tok = m.capture_decode(tok, 3)                 # 3 eager steps with device-side lengths, then capture
+    toks.append(tok)
+    for _ in range(17):
+        tok = m.decode_replay(tok)
+        toks.append(tok)
+    assert m.T == 41 and int(m.seq_lens[0]) == 41
+    got = torch.stack(toks, 1)
+    # column 1 holds the token after the 3 warm-up steps = eager column 3
+    assert torch.equal(got[:, 0], eager[:, 0]) and torch.equal(got[:, 1:], eager[:, 3:])
+    for La, Lb in zip(me.layers, m.layers):
+        assert torch.equal(La["kc"], Lb["kc"]) and torch.equal(La["vc"], Lb["vc"])

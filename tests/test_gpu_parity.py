@@ -214,6 +214,40 @@ def test_decode_with_scales_at_both_clamps(bits):
     assert np.array_equal(dk.cpu().numpy(), wk) and np.array_equal(dv.cpu().numpy(), wv)
 
 
+@pytest.mark.parametrize("bits,Hq,Hkv", [(4, 2, 2), (2, 4, 2)])
+def test_decode_varlen_ragged_batch(bits, Hq, Hkv):
+    """Per-sequence lengths on the device: every sequence must match a fixed-length call on itself alone."""
+    B, D, Tmax = 4, 128, 150
+    lens = [0, 37, 150, 96]
+    case = make_case(640, B, Hq, Hkv, Tmax, bits)
+    kp, vp = dev(case["kp"]), dev(case["vp"])
+    ns = orc.n_super_for(Tmax + 1, bits)
+    kc = torch.zeros(orc.cache_shape(B, Hkv, ns, D), dtype=torch.uint8, device="cuda")
+    vc = torch.zeros_like(kc)
+    for b, T in enumerate(lens):
+        if T:
+            gemv.encode_kv_pair(kc[b:b + 1], dev(case["k"][b:b + 1, :, :T]), kp, vc[b:b + 1],
+                                dev(case["v"][b:b + 1, :, :T]), vp, SMIN, SMAX, bits=bits)
+    k_ref, v_ref = kc.clone(), vc.clone()
+    kn = torch.stack([case["k"][b, :, T:T + 1] for b, T in enumerate(lens)]).cuda()
+    vn = torch.stack([case["v"][b, :, T:T + 1] for b, T in enumerate(lens)]).cuda()
+    q = dev(case["q"])
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    got = gemv.decode_attn_varlen(q, kc, vc, kn, vn, kp, vp, sl, 0.09, SMIN, SMAX, bits=bits)
+    for b, T in enumerate(lens):
+        want = gemv.decode_attn(q[b:b + 1], k_ref[b:b + 1], v_ref[b:b + 1], kn[b:b + 1], vn[b:b + 1], kp, vp, T, 0.09,
+                                SMIN, SMAX, bits=bits)
+        assert torch.equal(got[b:b + 1], want)
+    assert torch.equal(kc, k_ref) and torch.equal(vc, v_ref)
+    _status_ok()
+    # a length beyond the cache is reported through the status word and that stream is left alone
+    sl2 = torch.tensor([0, 37, ns * (32 // bits), 96], dtype=torch.int32, device="cuda")
+    before = kc.clone()
+    gemv.decode_attn_varlen(q, kc, vc, kn, vn, kp, vp, sl2, 0.09, SMIN, SMAX, bits=bits)
+    assert gemv.device_status() == 6
+    assert torch.equal(kc[2], before[2])
+
+
 def test_decode_steps_chain_like_generation():
     """Prefill with the kernel, then 40 fused decode steps; caches stay bit-identical to the oracle's."""
     B, H, T0, steps, bits, D = 2, 2, 21, 40, 4, 128
