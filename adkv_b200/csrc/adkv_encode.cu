@@ -10,29 +10,65 @@ namespace adkv {
 // (half2 per lane) and per supergroup it writes 256 contiguous bytes (uint2 per lane).  The next
 // word's tokens are fetched while the current word is quantised.
 constexpr int kEncThreads = kD / 2;
-constexpr int kEncStages = 4;   // 32-token (8 KB) tiles of fp16 input in flight per CTA
+constexpr int kEncStages = 3;   // 32-token (8 KB) tiles of fp16 input in flight per CTA; 24 KB lets 7+ CTAs share an SM,
+                                // so K and V of 512 streams (1024 CTAs) run as a single wave on 148 SMs
 
 // Eight tokens (fields J0 .. J0+7 of the word being assembled) for the two channels of a thread,
-// speculative quantiser; returns true when some code is in doubt and the group must be redone.
+// speculative quantiser (see quantize_spec) on the channel pair with packed fp32 arithmetic: half the
+// issue slots for the adds and multiplies, every element rounded exactly as by the scalar instruction.
+// Min/max, the reciprocal and the compare have no packed form and stay scalar.  Returns true when some
+// code is in doubt and the group must be redone with the exactly rounded division.
 template <int BITS, bool GUARDED, int J0>
 __device__ __forceinline__ bool encode_group(const __half2 *xin /* 8 rows of kD/2 */, Chan (&ch)[2],
-                                             uint32_t (&word)[2], float smin, float smax)
+                                             uint32_t (&word)[2], float smin, float smax, f32x2 one)
 {
     using C = Codec<BITS>;
+    constexpr float M = 12582912.f;   // 1.5 * 2^23
     bool doubt = !(ch[0].s < 1e29f) || !(ch[1].s < 1e29f);   // reciprocal would flush to zero
+    f32x2 zp = pk2(ch[0].zp, ch[1].zp), s = pk2(ch[0].s, ch[1].s);
+    const f32x2 alpha = pk2(ch[0].alpha, ch[1].alpha), beta = pk2(ch[0].beta, ch[1].beta);
+    const f32x2 neg_t = pk2(-ch[0].tc, -ch[1].tc), m2 = pk2(M, M);
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
-        const float2 x = __half22float2(xin[j * (kD / 2)]);
-        const float xs[2] = {x.x, x.y};
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            float rh;
-            uint32_t tb;
-            const float q = quantize_spec<BITS, GUARDED>(xs[c], ch[c], rh, tb, doubt);
-            advance_canonical_g<GUARDED>(q, rh, ch[c], smin, smax);
-            word[c] |= ((tb & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
+        const float2 xf = __half22float2(xin[j * (kD / 2)]);
+        float s0, s1;
+        upk2(s, s0, s1);
+        if (GUARDED) {
+            s0 = fmaxf(s0, kEps);
+            s1 = fmaxf(s1, kEps);
+        }
+        const f32x2 ss = GUARDED ? pk2(s0, s1) : s;
+        float i0, i1;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(i0) : "f"(s0));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(i1) : "f"(s1));
+        const f32x2 v = mul2(sub2(pk2(xf.x, xf.y), zp), pk2(i0, i1));
+        float v0, v1;
+        upk2(v, v0, v1);
+        const f32x2 vc = pk2(fminf(fmaxf(v0, C::qlo()), C::qhi()), fminf(fmaxf(v1, C::qlo()), C::qhi()));
+        const f32x2 t = add2(vc, m2);
+        const f32x2 q = sub2(t, m2);
+        float d0, d1;
+        upk2(sub2(vc, q), d0, d1);
+        // clamped quotient within 4e-6 of a rounding boundary: cannot tell which way the exact one rounds
+        doubt |= !(fabsf(d0) < 0.5f - 4e-6f) || !(fabsf(d1) < 0.5f - 4e-6f);
+        const f32x2 rh = mul2(q, ss);
+        uint32_t t0, t1;
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(t0), "=r"(t1) : "l"(t));
+        word[0] |= ((t0 & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
+        word[1] |= ((t1 & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
+        // state update, canonical order (products are added as fma(x, 1, y): see add_product2)
+        zp = add_product2(mul2(alpha, rh), one, zp);
+        const f32x2 s_new = add_product2(mul2(mul2(s, beta), add2(abs2(q), neg_t)), one, s);
+        if (GUARDED) {
+            float n0, n1;
+            upk2(s_new, n0, n1);
+            s = pk2(fminf(fmaxf(n0, smin), smax), fminf(fmaxf(n1, smin), smax));
+        } else {
+            s = s_new;
         }
     });
+    upk2(zp, ch[0].zp, ch[1].zp);
+    upk2(s, ch[0].s, ch[1].s);
     return doubt;
 }
 
@@ -84,6 +120,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     }
     SafeRange safe;
     safe.template init<BITS, 2>(beta, target, smin, smax);
+    const f32x2 one = opaque_ones2();
 
     __shared__ alignas(128) __half buf[kEncStages][32 * kD];
     __shared__ uint64_t bar[kEncStages];
@@ -174,11 +211,11 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
             const bool second = C::TPW == 16 && (t & 8);
             bool doubt;
             if (safe.holds(ch)) {
-                doubt = second ? encode_group<BITS, false, 8 % C::TPW>(rows, ch, word, smin, smax)
-                               : encode_group<BITS, false, 0>(rows, ch, word, smin, smax);
+                doubt = second ? encode_group<BITS, false, 8 % C::TPW>(rows, ch, word, smin, smax, one)
+                               : encode_group<BITS, false, 0>(rows, ch, word, smin, smax, one);
             } else {
-                doubt = second ? encode_group<BITS, true, 8 % C::TPW>(rows, ch, word, smin, smax)
-                               : encode_group<BITS, true, 0>(rows, ch, word, smin, smax);
+                doubt = second ? encode_group<BITS, true, 8 % C::TPW>(rows, ch, word, smin, smax, one)
+                               : encode_group<BITS, true, 0>(rows, ch, word, smin, smax, one);
             }
             if (doubt) {   // rare, per thread: redo the group from the saved state with the exact quantiser
                 ch[0] = saved[0];
