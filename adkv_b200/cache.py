@@ -11,7 +11,9 @@ from token 0, decode one token at a time), on top of the B200 kernels.  Differen
   ``decode`` returns ``None`` in their place.  ``fused=False`` reproduces the reference's sequence;
 * grouped-query attention (more query heads than KV heads), which the reference rejects
   (``llama_adkv.py:235-238``);
-* ``bits`` = 4 (reference layout) or 2.
+* ``bits`` = 4 (reference layout) or 2;
+* ``checkpoint_interval`` (with ``capacity_tokens``): keep recurrence-state checkpoints every that many tokens
+  and decode with one warp pair per segment instead of one per sequence (long contexts, small batches).
 """
 from __future__ import annotations
 
@@ -25,10 +27,15 @@ CAP_LEN = 64        # src/adkv/hf/llama_adkv.py:41
 
 
 class KVCacheLayer:
-    def __init__(self, bits: int = 4, fused: bool = True, fast: bool = False, capacity_tokens: int | None = None):
+    def __init__(self, bits: int = 4, fused: bool = True, fast: bool = False, capacity_tokens: int | None = None,
+                 checkpoint_interval: int = 0):
         if bits not in (2, 4):
             raise ValueError("bits must be 2 or 4")
+        if checkpoint_interval and (not capacity_tokens or not fused or checkpoint_interval % 32):
+            raise ValueError("checkpoints need a fused cache with capacity_tokens and an interval that is a multiple of 32")
         self.bits, self.fused, self.fast = bits, fused, fast
+        self._ckpt_interval = checkpoint_interval
+        self._kck = self._vck = None
         self._tpw = 32 // bits
         self._capacity_tokens = capacity_tokens
         self._key_buf = None
@@ -63,6 +70,14 @@ class KVCacheLayer:
         shape = (self._B, self._H, n_super, self._C // 4, 4, 4)
         self._key_buf = torch.zeros(shape, dtype=torch.uint8, device=self._device)
         self._value_buf = torch.zeros(shape, dtype=torch.uint8, device=self._device)
+        if self._ckpt_interval and self._kck is None:
+            self._kck = gemv.alloc_ckpt(self._B, self._H, self._C, self._capacity_tokens, self._ckpt_interval, self._device)
+            self._vck = gemv.alloc_ckpt(self._B, self._H, self._C, self._capacity_tokens, self._ckpt_interval, self._device)
+
+    def _ckpt_kwargs(self):
+        if not self._ckpt_interval:
+            return {}
+        return dict(k_ckpt=self._kck, v_ckpt=self._vck, ckpt_interval=self._ckpt_interval)
 
     def _init_buffers(self, B: int, H: int, C: int, device):
         if C != 128:
@@ -75,6 +90,8 @@ class KVCacheLayer:
         """Grow by CAP_LEN slots until at least ``T`` tokens fit (copying the old contents)."""
         if T <= self._cap_len:
             return
+        if self._ckpt_interval:
+            raise ValueError(f"checkpointed cache is sized once: {T} tokens exceed capacity_tokens {self._cap_len}")
         new_cap = self._cap_len
         while new_cap < T:
             new_cap += CAP_LEN
@@ -108,7 +125,7 @@ class KVCacheLayer:
                             (v(key_zp_init), v(key_scale_init), v(key_alpha), v(key_beta), v(key_quant_target)),
                             self._value_buf, value,
                             (v(value_zp_init), v(value_scale_init), v(value_alpha), v(value_beta),
-                             v(value_quant_target)), SCALE_MIN, SCALE_MAX, bits=self.bits)
+                             v(value_quant_target)), SCALE_MIN, SCALE_MAX, bits=self.bits, **self._ckpt_kwargs())
         self._quant_len += T
 
     # ------------------------------------------------------------------ decode
@@ -141,9 +158,12 @@ class KVCacheLayer:
         mask = None
         if attention_mask is not None:
             mask = attention_mask[:, :, 0, :] if attention_mask.dim() == 4 else attention_mask
+        if self._ckpt_interval and not (mask is None or mask.numel() == B * (ctx_len + 1)):
+            raise ValueError("a checkpointed cache takes masks shared by all heads only")
         if self.fused and (mask is None or mask.numel() == B * (ctx_len + 1)):
             out = gemv.decode_attn(q, self._key_buf, self._value_buf, k, v, kp, vp, ctx_len, scaling,
-                                   SCALE_MIN, SCALE_MAX, mask=mask, bits=self.bits, fast=self.fast)
+                                   SCALE_MIN, SCALE_MAX, mask=mask, bits=self.bits, fast=self.fast,
+                                   **self._ckpt_kwargs())
             weights = None
         else:
             logits = gemv.forward_qk(q, self._key_buf, k, *kp, ctx_len, SCALE_MIN, SCALE_MAX,

@@ -57,6 +57,24 @@ def test_generation_across_growth_boundaries(bits, Hq, Hkv):
         torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=3e-2 * float(a.abs().max()))
 
 
+def test_checkpointed_cache_object_matches_plain():
+    B, H, D, T0, steps, bits = 2, 2, 128, 70, 40, 4
+    k = synth.gen_kv(11, B, H, T0 + steps, D)
+    v = synth.gen_kv(12, B, H, T0 + steps, D)
+    kp, vp = synth.gen_params(13, H, D, bits), synth.gen_params(14, H, D, bits)
+    g = torch.Generator().manual_seed(2)
+    q_all = [torch.randn(B, H, 1, D, generator=g).half() for _ in range(steps)]
+    plain = KVCacheLayer(bits=bits, capacity_tokens=T0 + steps)
+    ck = KVCacheLayer(bits=bits, capacity_tokens=T0 + steps, checkpoint_interval=32)
+    o1 = _run(plain, k, v, q_all, kp, vp, T0, steps, 0.09)
+    o2 = _run(ck, k, v, q_all, kp, vp, T0, steps, 0.09)
+    assert torch.equal(plain.key_states, ck.key_states) and torch.equal(plain.value_states, ck.value_states)
+    for a, b in zip(o1, o2):
+        torch.testing.assert_close(a.float(), b.float(), rtol=2e-3, atol=2e-3 * max(1.0, float(a.abs().max())))
+    with pytest.raises(ValueError, match="capacity_tokens"):
+        KVCacheLayer(checkpoint_interval=32)
+
+
 def test_cache_object_errors_match_reference_behaviour():
     layer = KVCacheLayer()
     x = torch.zeros(1, 2, 4, 128, dtype=torch.float16, device="cuda")
