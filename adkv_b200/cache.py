@@ -80,8 +80,10 @@ class KVCacheLayer:
         return dict(k_ckpt=self._kck, v_ckpt=self._vck, ckpt_interval=self._ckpt_interval)
 
     def _init_buffers(self, B: int, H: int, C: int, device):
-        if C != 128:
-            raise ValueError(f"ADKV kernels of this build support head_dim 128, got {C}")
+        if C not in (128, 256, 512):
+            raise ValueError(f"ADKV kernels support head_dim in (128, 256, 512), got {C}")
+        if C != 128 and self._ckpt_interval:
+            raise ValueError("state checkpoints are available for head_dim 128 only")
         self._B, self._H, self._C, self._device = B, H, C, device
         self._quant_len = 0
         self._alloc(max(INIT_SEQ_LEN, self._capacity_tokens or 0))

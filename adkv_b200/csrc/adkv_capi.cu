@@ -6,6 +6,7 @@ ADKV_HIDDEN int adkv_tu_status_fused(int *out);
 ADKV_HIDDEN int adkv_tu_status_unfused(int *out);
 ADKV_HIDDEN int adkv_tu_status_encode(int *out);
 ADKV_HIDDEN int adkv_tu_status_split(int *out);
+ADKV_HIDDEN int adkv_tu_status_wide(int *out);
 
 extern "C" {
 
@@ -16,9 +17,9 @@ const char *adkv_strerror(int code)
     switch (code) {
     case 0: return "success";
     case ADKV_E_NULL: return "adkv: a required pointer is NULL";
-    case ADKV_E_HEAD_DIM: return "adkv: head dim not supported by this build (D must be 128)";
+    case ADKV_E_HEAD_DIM: return "adkv: head dim not supported (128, 256 or 512; checkpointed and device-length decode: 128)";
     case ADKV_E_BITS: return "adkv: bits must be 2 or 4";
-    case ADKV_E_SHAPE: return "adkv: invalid sizes (negative, Hq not a multiple of Hkv, or group size not in {1,2,4,8})";
+    case ADKV_E_SHAPE: return "adkv: invalid sizes (negative, Hq not a multiple of Hkv, or group size not in {1,2,4,8}; {1,2} for head dims 256/512)";
     case ADKV_E_CAPACITY: return "adkv: cache capacity too small for the tokens to be written";
     case ADKV_E_ALIGN: return "adkv: pointer not sufficiently aligned (cache 16 bytes, fp16 rows 8 bytes)";
     case ADKV_E_START: return "adkv: t_start > 0 needs a tail state";
@@ -35,12 +36,13 @@ int adkv_device_status(int *status, void *stream)
     if (!status) return ADKV_E_NULL;
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return int(e);
-    int a = 0, b = 0, c = 0, d = 0;
+    int a = 0, b = 0, c = 0, d = 0, w = 0;
     if (int rc = adkv_tu_status_fused(&a)) return rc;
     if (int rc = adkv_tu_status_unfused(&b)) return rc;
     if (int rc = adkv_tu_status_encode(&c)) return rc;
     if (int rc = adkv_tu_status_split(&d)) return rc;
-    *status = a ? a : (b ? b : (c ? c : d));
+    if (int rc = adkv_tu_status_wide(&w)) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : w)));
     return 0;
 }
 

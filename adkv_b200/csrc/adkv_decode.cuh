@@ -28,13 +28,14 @@ struct Tile {
 };
 
 // Per-warp bulk-copy ring over the words of one stream.
-template <int BITS>
+template <int BITS, int STAGES = kStages>
 struct StreamRing {
-    uint8_t *buf;           // kStages * Tile::BYTES, 128-byte aligned
-    uint64_t *bar;          // kStages barriers
-    const uint8_t *src;     // start of the stream in global memory
+    uint8_t *buf;           // STAGES * Tile::BYTES, 128-byte aligned
+    uint64_t *bar;          // STAGES barriers
+    const uint8_t *src;     // first word row of this warp's 128-channel slice of the stream
     int n_tiles, T;
     int wait_code;
+    uint32_t row_stride;    // bytes between word rows in global memory: 4 * head_dim (512 = contiguous slice)
 
     __device__ __forceinline__ uint32_t tile_bytes(int i) const
     {
@@ -45,37 +46,43 @@ struct StreamRing {
     // lane 0 only
     __device__ __forceinline__ void issue(int i) const
     {
-        const int st = i % kStages;
+        const int st = i % STAGES;
         const uint32_t bytes = tile_bytes(i);
         mbar_expect_tx(&bar[st], bytes);
-        bulk_load(buf + st * Tile<BITS>::BYTES, src + size_t(i) * Tile<BITS>::BYTES, bytes, &bar[st]);
+        if (row_stride == kD * 4) {
+            bulk_load(buf + st * Tile<BITS>::BYTES, src + size_t(i) * Tile<BITS>::BYTES, bytes, &bar[st]);
+        } else {   // head_dim > 128: the slice's 512-byte rows are strided, one copy per row
+            const uint8_t *row = src + size_t(i) * Tile<BITS>::WORDS * row_stride;
+            for (uint32_t off = 0; off < bytes; off += kD * 4, row += row_stride)
+                bulk_load(buf + st * Tile<BITS>::BYTES + off, row, kD * 4, &bar[st]);
+        }
     }
     __device__ __forceinline__ void prologue(int lane) const
     {
         if (lane == 0)
-            for (int i = 0; i < min(kStages, n_tiles); ++i) issue(i);
+            for (int i = 0; i < min(STAGES, n_tiles); ++i) issue(i);
     }
     __device__ __forceinline__ bool wait(int i) const
     {
-        return mbar_wait_bounded(&bar[i % kStages], (i / kStages) & 1, wait_code);
+        return mbar_wait_bounded(&bar[i % STAGES], (i / STAGES) & 1, wait_code);
     }
     __device__ __forceinline__ const uint4 *tile(int i, int lane) const
     {
-        return reinterpret_cast<const uint4 *>(buf + (i % kStages) * Tile<BITS>::BYTES) + lane;
+        return reinterpret_cast<const uint4 *>(buf + (i % STAGES) * Tile<BITS>::BYTES) + lane;
     }
     // all lanes, after the tile has been consumed
     __device__ __forceinline__ void release_and_refill(int i, int lane) const
     {
         __syncwarp();
-        if (lane == 0 && i + kStages < n_tiles) issue(i + kStages);
+        if (lane == 0 && i + STAGES < n_tiles) issue(i + STAGES);
     }
     // After a failed wait: give copies already issued a bounded chance to land before the
     // shared memory is handed back.
     __device__ __forceinline__ void drain(int from) const
     {
-        const int issued = min(n_tiles, from + kStages);
+        const int issued = min(n_tiles, from + STAGES);
         for (int i = from; i < issued; ++i)
-            if (!mbar_wait_bounded(&bar[i % kStages], (i / kStages) & 1, kStatDrain)) break;
+            if (!mbar_wait_bounded(&bar[i % STAGES], (i / STAGES) & 1, kStatDrain)) break;
     }
 };
 
@@ -177,30 +184,31 @@ __device__ __forceinline__ void reduce8(const float *red, int lane, float (&sum)
     __syncwarp();
 }
 
-// The part of a stream one warp pair works on.  The whole-stream kernels use {0, T, true, nullptr, nullptr};
+// The part of a stream one warp pair works on.  The whole-stream kernels use {0, T, true, nullptr, nullptr, 0};
 // the checkpointed kernel gives every segment its own pair of warps.
 struct Seg {
     int t_begin;          // first token replayed (a multiple of kTileTok)
     int t_end;            // one past the last token replayed
     bool append;          // quantise x_new as token t_end (== T), write it, add its own term
-    const float *init;    // state before token t_begin of this stream, [2][kD] (zp, scale); nullptr = parameters
-    float *ckpt_out;      // where to store the state after the appended token, [2][kD]; nullptr = nowhere
+    const float *init;    // state before token t_begin of this stream, [2][head_dim] (zp, scale); nullptr = parameters
+    float *ckpt_out;      // where to store the state after the appended token, [2][head_dim]; nullptr = nowhere
+    int slice;            // which 128-channel slice of the head this warp owns (0 for head_dim 128)
 };
 
-__device__ __forceinline__ void load_init_state(Chan (&ch)[4], const float *init, int lane)
+__device__ __forceinline__ void load_init_state(Chan (&ch)[4], const float *init, int c0, int D)
 {
     if (init) {
-        const float4 zp = *reinterpret_cast<const float4 *>(init + 4 * lane);
-        const float4 sc = *reinterpret_cast<const float4 *>(init + kD + 4 * lane);
+        const float4 zp = *reinterpret_cast<const float4 *>(init + c0);
+        const float4 sc = *reinterpret_cast<const float4 *>(init + D + c0);
         ch[0].zp = zp.x; ch[1].zp = zp.y; ch[2].zp = zp.z; ch[3].zp = zp.w;
         ch[0].s = sc.x; ch[1].s = sc.y; ch[2].s = sc.z; ch[3].s = sc.w;
     }
 }
 
-__device__ __forceinline__ void store_state(float *dst, const Chan (&ch)[4], int lane)
+__device__ __forceinline__ void store_state(float *dst, const Chan (&ch)[4], int c0, int D)
 {
-    *reinterpret_cast<float4 *>(dst + 4 * lane) = make_float4(ch[0].zp, ch[1].zp, ch[2].zp, ch[3].zp);
-    *reinterpret_cast<float4 *>(dst + kD + 4 * lane) = make_float4(ch[0].s, ch[1].s, ch[2].s, ch[3].s);
+    *reinterpret_cast<float4 *>(dst + c0) = make_float4(ch[0].zp, ch[1].zp, ch[2].zp, ch[3].zp);
+    *reinterpret_cast<float4 *>(dst + D + c0) = make_float4(ch[0].s, ch[1].s, ch[2].s, ch[3].s);
 }
 
 struct KArgs {
@@ -210,6 +218,7 @@ struct KArgs {
     ParamPtrs p;
     int Hq, Hkv, T, n_super_cap;
     float smin, smax;
+    int D;                  // head dim (128, 256 or 512)
 };
 
 // Sink interface (duck-typed):
@@ -218,21 +227,22 @@ struct KArgs {
 //   void end_tile(int i, int lane)
 //   void put_self(int g, float v)     lane 0
 //   void finish(int lane)
-template <int BITS, int G, bool EXACT, class Sink>
+template <int BITS, int G, bool EXACT, class Sink, int STAGES = kStages>
 __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, float *red, Sink &sink)
 {
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
+    const int c0 = kD * seg.slice + 4 * lane;      // first of this lane's 4 channels within the head
     Chan ch[4];
     SafeRange safe;
     FieldConsts<BITS> fc;
     fc.init();
-    load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
-    load_init_state(ch, seg.init, lane);
+    load_chan4<BITS, EXACT>(ch, safe, a.p, size_t(h) * a.D + c0, a.smin, a.smax);
+    load_init_state(ch, seg.init, c0, a.D);
     float qv[G][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane);
+    for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * a.D + c0);
     PairConst pc[2];
     make_pair_consts<EXACT>(ch, pc);
     const f32x2 one = opaque_ones2();   // read once: a constant-memory load per chunk would stall the chain
@@ -243,10 +253,11 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
         qv2[g][1] = pk2(qv[g][2], qv[g][3]);
     }
 
-    uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
+    const uint32_t row_stride = uint32_t(a.D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * a.D + size_t(kD) * seg.slice) * 4;
     const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * kD * 4,
-                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait};
+    StreamRing<BITS, STAGES> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait, row_stride};
     ring.prologue(lane);
 
     bool ok = true;
@@ -302,8 +313,8 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
     // Append k_new as token T with the state left by token T-1, then its own logit from the
     // dequantised value.
     float xn[4], xh[4];
-    load_half4(xn, a.x_new + size_t(bh) * kD + 4 * lane);
-    uint4 *slot = reinterpret_cast<uint4 *>(stream) + size_t(a.T / C::TPW) * (kD / 4) + lane;
+    load_half4(xn, a.x_new + size_t(bh) * a.D + c0);
+    uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
     uint4 wv = *slot;
     uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
     const int sh = BITS * (a.T % C::TPW);
@@ -316,7 +327,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
         if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
     }
     *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
-    if (seg.ckpt_out) store_state(seg.ckpt_out, ch, lane);
+    if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, a.D);
     if (!sink.begin_tile(ring.n_tiles)) return;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -419,6 +430,7 @@ struct VArgs {
     ParamPtrs p;
     int Hq, Hkv, T, n_super_cap;
     float smin, smax;
+    int D;                  // head dim (128, 256 or 512)
 };
 
 // Source interface (duck-typed):
@@ -426,19 +438,20 @@ struct VArgs {
 //        fill wts[g][0..31] for tile i (0 for tokens >= ntok); may rescale acc (online softmax);
 //        false = bounded wait gave up
 //   bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
-//   void store(const VArgs&, int b, int h, int lane, const float (&acc)[G][4])   write the result
-template <int BITS, int G, bool EXACT, class Src>
+//   void store(const VArgs&, int b, int h, int c0, const float (&acc)[G][4])   write the result (c0: first channel)
+template <int BITS, int G, bool EXACT, class Src, int STAGES = kStages>
 __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, const float2 *wts, Src &src)
 {
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
+    const int c0 = kD * seg.slice + 4 * lane;
     Chan ch[4];
     SafeRange safe;
     FieldConsts<BITS> fc;
     fc.init();
-    load_chan4<BITS, EXACT>(ch, safe, a.p, h, 4 * lane, a.smin, a.smax);
-    load_init_state(ch, seg.init, lane);
+    load_chan4<BITS, EXACT>(ch, safe, a.p, size_t(h) * a.D + c0, a.smin, a.smax);
+    load_init_state(ch, seg.init, c0, a.D);
     PairConst pc[2];
     make_pair_consts<EXACT>(ch, pc);
     const f32x2 one = opaque_ones2();   // read once: a constant-memory load per chunk would stall the chain
@@ -448,10 +461,11 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
 
-    uint8_t *stream = a.cache + size_t(bh) * a.n_super_cap * kD * 4;
+    const uint32_t row_stride = uint32_t(a.D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * a.D + size_t(kD) * seg.slice) * 4;
     const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * kD * 4,
-                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait};
+    StreamRing<BITS, STAGES> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait, row_stride};
     ring.prologue(lane);
 
     bool ok = true;
@@ -499,8 +513,8 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
         float w_self[G];
         if (!src.self_weight(lane, acc, w_self, a.T)) return;
         float xn[4], xh[4];
-        load_half4(xn, a.x_new + size_t(bh) * kD + 4 * lane);
-        uint4 *slot = reinterpret_cast<uint4 *>(stream) + size_t(a.T / C::TPW) * (kD / 4) + lane;
+        load_half4(xn, a.x_new + size_t(bh) * a.D + c0);
+        uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
         uint4 wv = *slot;
         uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
         const int sh = BITS * (a.T % C::TPW);
@@ -513,18 +527,18 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
             if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
         }
         *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
-        if (seg.ckpt_out) store_state(seg.ckpt_out, ch, lane);
+        if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, a.D);
 #pragma unroll
         for (int g = 0; g < G; ++g)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[g][c] = fmaf(w_self[g], xh[c], acc[g][c]);
     }
-    src.store(a, b, h, lane, acc);
+    src.store(a, b, h, c0, acc);
 }
 
 // Final division by the softmax denominator and fp16 store of the 4 channels of every head.
 template <int G, class Src>
-__device__ __forceinline__ void store_normalised(const Src &src, const VArgs &a, int b, int h, int lane,
+__device__ __forceinline__ void store_normalised(const Src &src, const VArgs &a, int b, int h, int c0,
                                                  const float (&acc)[G][4])
 {
 #pragma unroll
@@ -533,7 +547,7 @@ __device__ __forceinline__ void store_normalised(const Src &src, const VArgs &a,
         float o[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[c] = acc[g][c] * inv;
-        store_half4(a.out + (size_t(b) * a.Hq + size_t(h) * G + g) * kD + 4 * lane, o);
+        store_half4(a.out + (size_t(b) * a.Hq + size_t(h) * G + g) * a.D + c0, o);
     }
 }
 

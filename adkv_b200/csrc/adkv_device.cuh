@@ -429,16 +429,15 @@ __device__ __forceinline__ float warp_max(float v)
     return v;
 }
 
-// Load the five fp16 parameters of 4 consecutive channels starting at `c0` of kv head `h`.
+// Load the five fp16 parameters of 4 consecutive channels starting at element `off` of the [Hkv, D] tensors.
 struct ParamPtrs {
     const __half *zp_init, *scale_init, *alpha, *beta, *target;
 };
 
 template <int BITS, bool EXACT>
-__device__ __forceinline__ void load_chan4(Chan (&ch)[4], SafeRange &safe, const ParamPtrs &p, int h, int c0,
+__device__ __forceinline__ void load_chan4(Chan (&ch)[4], SafeRange &safe, const ParamPtrs &p, size_t off,
                                            float smin, float smax)
 {
-    const size_t off = size_t(h) * kD + c0;
     const uint2 a = *reinterpret_cast<const uint2 *>(p.zp_init + off);
     const uint2 b = *reinterpret_cast<const uint2 *>(p.scale_init + off);
     const uint2 c = *reinterpret_cast<const uint2 *>(p.alpha + off);

@@ -78,11 +78,12 @@ struct EncTensor {
     const __half *x;
     ParamPtrs p;
     float *tail;
-    float *ckpt;   // state checkpoints [B*H][n_ckpt_cap][2][kD] or nullptr; entry k = state before token (k+1)*interval
+    float *ckpt;   // state checkpoints [B*H][n_ckpt_cap][2][D] or nullptr; entry k = state before token (k+1)*interval
 };
 struct CkptSpec {
     int interval;     // tokens between checkpoints (multiple of 32), 0 = none
     int n_ckpt_cap;
+    int D;            // head dim (128, 256 or 512); a CTA handles one 128-channel slice of one stream
 };
 struct EncBatch {
     EncTensor t[2];
@@ -98,8 +99,9 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     const __half *__restrict__ x = et.x;
     const ParamPtrs p = et.p;
     float *__restrict__ tail = et.tail;
-    const int bh = blockIdx.x, h = bh % H, c0 = 2 * threadIdx.x;
-    const size_t po = size_t(h) * kD + c0;
+    const int D = cs.D, S = D / kD;
+    const int bh = blockIdx.x / S, h = bh % H, c0 = kD * (blockIdx.x % S) + 2 * threadIdx.x;   // c0: channel in the head
+    const size_t po = size_t(h) * D + c0;
     Chan ch[2];
     float beta[2], target[2];
     {
@@ -108,8 +110,8 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
         const float2 tg = __half22float2(*reinterpret_cast<const __half2 *>(p.target + po));
         float2 zp, sc;
         if (t_start > 0) {
-            zp = *reinterpret_cast<const float2 *>(tail + size_t(bh) * 2 * kD + c0);
-            sc = *reinterpret_cast<const float2 *>(tail + size_t(bh) * 2 * kD + kD + c0);
+            zp = *reinterpret_cast<const float2 *>(tail + size_t(bh) * 2 * D + c0);
+            sc = *reinterpret_cast<const float2 *>(tail + size_t(bh) * 2 * D + D + c0);
         } else {
             zp = __half22float2(*reinterpret_cast<const __half2 *>(p.zp_init + po));
             sc = __half22float2(*reinterpret_cast<const __half2 *>(p.scale_init + po));
@@ -130,9 +132,10 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     }
     __syncthreads();
 
-    uint2 *w = reinterpret_cast<uint2 *>(cache + size_t(bh) * n_super_cap * kD + c0);       // stride kD/2 per word row
-    const __half2 *xs = reinterpret_cast<const __half2 *>(x + size_t(bh) * T * kD + c0);    // stride kD/2 per token
-    constexpr int RS = kD / 2;
+    uint2 *w = reinterpret_cast<uint2 *>(cache + size_t(bh) * n_super_cap * D + c0);       // stride D/2 per word row
+    const __half2 *xs = reinterpret_cast<const __half2 *>(x + size_t(bh) * T * D + c0);    // stride D/2 per token
+    const int RS = D / 2;          // row stride in global memory (uint2 words / half2 inputs)
+    constexpr int SRS = kD / 2;    // row stride of the staged slice in shared memory
 
     // one token with a run-time field position, exactly rounded division (partial words, redone groups)
     auto exact_token = [&](int t, uint32_t(&word)[2]) {
@@ -148,14 +151,14 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     };
 
     // checkpoint k is written when the state before token (k+1)*interval is reached
-    float *ckpt = (et.ckpt && cs.interval > 0) ? et.ckpt + size_t(bh) * cs.n_ckpt_cap * 2 * kD + c0 : nullptr;
+    float *ckpt = (et.ckpt && cs.interval > 0) ? et.ckpt + size_t(bh) * cs.n_ckpt_cap * 2 * D + c0 : nullptr;
     int next_ckpt = ckpt ? (t_start / cs.interval + 1) * cs.interval : 0x7fffffff;
     auto checkpoint = [&](int t_reached) {
         if (t_reached == next_ckpt) {
             const int k = next_ckpt / cs.interval - 1;
             if (k < cs.n_ckpt_cap) {
-                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * kD) = make_float2(ch[0].zp, ch[1].zp);
-                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * kD + kD) = make_float2(ch[0].s, ch[1].s);
+                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * D) = make_float2(ch[0].zp, ch[1].zp);
+                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * D + D) = make_float2(ch[0].s, ch[1].s);
             }
             next_ckpt += cs.interval;
         }
@@ -185,11 +188,17 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     // the quantiser by kEncStages - 1 tiles.
     const int n_groups = (t_end - t) / 8;
     const int n_tiles = (n_groups + 3) / 4;
-    const __half *src = x + (size_t(bh) * T + (t - t_start)) * kD;
+    const __half *src = x + (size_t(bh) * T + (t - t_start)) * D + kD * (blockIdx.x % S);
     auto issue = [&](int i) {
-        const uint32_t bytes = uint32_t(min(4, n_groups - 4 * i)) * 8 * kD * 2;
+        const int rows = min(4, n_groups - 4 * i) * 8;
+        const uint32_t bytes = uint32_t(rows) * kD * 2;
         mbar_expect_tx(&bar[i % kEncStages], bytes);
-        bulk_load(&buf[i % kEncStages][0], src + size_t(i) * 32 * kD, bytes, &bar[i % kEncStages]);
+        if (S == 1) {
+            bulk_load(&buf[i % kEncStages][0], src + size_t(i) * 32 * kD, bytes, &bar[i % kEncStages]);
+        } else {   // the slice's 256-byte rows are strided in global memory: one copy per token row
+            for (int r = 0; r < rows; ++r)
+                bulk_load(&buf[i % kEncStages][r * kD], src + (size_t(i) * 32 + r) * D, kD * 2, &bar[i % kEncStages]);
+        }
     };
     if (threadIdx.x == 0)
         for (int i = 0; i < min(kEncStages, n_tiles); ++i) issue(i);
@@ -205,7 +214,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
         const int ng = min(4, n_groups - 4 * i);
 #pragma unroll 1
         for (int g = 0; g < ng; ++g, t += 8) {
-            const __half2 *rows = reinterpret_cast<const __half2 *>(&buf[i % kEncStages][0]) + g * 8 * RS + threadIdx.x;
+            const __half2 *rows = reinterpret_cast<const __half2 *>(&buf[i % kEncStages][0]) + g * 8 * SRS + threadIdx.x;
             const Chan saved[2] = {ch[0], ch[1]};
             const uint32_t word_in[2] = {word[0], word[1]};
             const bool second = C::TPW == 16 && (t & 8);
@@ -240,8 +249,8 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     }
     if (t % C::TPW != 0) w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
     if (tail) {
-        *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * kD + c0) = make_float2(ch[0].zp, ch[1].zp);
-        *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * kD + kD + c0) = make_float2(ch[0].s, ch[1].s);
+        *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * D + c0) = make_float2(ch[0].zp, ch[1].zp);
+        *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * D + D + c0) = make_float2(ch[0].s, ch[1].s);
     }
 }
 
@@ -256,28 +265,29 @@ __global__ void __launch_bounds__(kD) append_kernel(EncBatch batch, CkptSpec cs,
     const __half *__restrict__ x_new = et.x;
     const ParamPtrs p = et.p;
     float *__restrict__ tail = et.tail;
-    const int bh = blockIdx.x, h = bh % H, c = threadIdx.x;
-    const size_t po = size_t(h) * kD + c;
+    const int D = cs.D, S = D / kD;
+    const int bh = blockIdx.x / S, h = bh % H, c = kD * (blockIdx.x % S) + threadIdx.x;
+    const size_t po = size_t(h) * D + c;
     Chan ch;
     ch.alpha = __half2float(p.alpha[po]);
     ch.beta = __half2float(p.beta[po]);
     ch.tc = __half2float(p.target[po]);
-    ch.zp = tail[size_t(bh) * 2 * kD + c];
-    ch.s = tail[size_t(bh) * 2 * kD + kD + c];
+    ch.zp = tail[size_t(bh) * 2 * D + c];
+    ch.s = tail[size_t(bh) * 2 * D + D + c];
     float rh;
-    const float q = quantize<BITS>(__half2float(x_new[size_t(bh) * kD + c]), ch, rh);
-    uint32_t *slot = cache + (size_t(bh) * n_super_cap + T / C::TPW) * kD + c;
+    const float q = quantize<BITS>(__half2float(x_new[size_t(bh) * D + c]), ch, rh);
+    uint32_t *slot = cache + (size_t(bh) * n_super_cap + T / C::TPW) * D + c;
     const int sh = BITS * (T % C::TPW);
     *slot = (*slot & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
     advance_canonical(q, rh, ch, smin, smax);
-    tail[size_t(bh) * 2 * kD + c] = ch.zp;
-    tail[size_t(bh) * 2 * kD + kD + c] = ch.s;
+    tail[size_t(bh) * 2 * D + c] = ch.zp;
+    tail[size_t(bh) * 2 * D + D + c] = ch.s;
     if (et.ckpt && cs.interval > 0 && (T + 1) % cs.interval == 0) {
         const int k = (T + 1) / cs.interval - 1;
         if (k < cs.n_ckpt_cap) {
-            float *dst = et.ckpt + (size_t(bh) * cs.n_ckpt_cap + k) * 2 * kD;
+            float *dst = et.ckpt + (size_t(bh) * cs.n_ckpt_cap + k) * 2 * D;
             dst[c] = ch.zp;
-            dst[kD + c] = ch.s;
+            dst[D + c] = ch.s;
         }
     }
 }
@@ -323,21 +333,23 @@ static int ckpt_check(const void *k_ckpt, const void *v_ckpt, int interval, int 
     return 0;
 }
 
-static int launch_encode(const EncBatch &b, int n, int B, int H, int T, int n_super_cap, int bits, int t_start,
-                         float smin, float smax, void *stream, CkptSpec cs = CkptSpec{0, 0})
+static int launch_encode(const EncBatch &b, int n, int B, int H, int T, int D, int n_super_cap, int bits,
+                         int t_start, float smin, float smax, void *stream, CkptSpec cs = CkptSpec{0, 0, 0})
 {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const dim3 grid(B * H, n);
+    cs.D = D;
+    const dim3 grid(B * H * (D / kD), n);
     if (bits == 4) encode_kernel<4><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
     else encode_kernel<2><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
     return launch_status();
 }
 
-static int launch_append(const EncBatch &b, int n, int B, int H, int T, int n_super_cap, int bits, float smin,
-                         float smax, void *stream, CkptSpec cs = CkptSpec{0, 0})
+static int launch_append(const EncBatch &b, int n, int B, int H, int T, int D, int n_super_cap, int bits,
+                         float smin, float smax, void *stream, CkptSpec cs = CkptSpec{0, 0, 0})
 {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const dim3 grid(B * H, n);
+    cs.D = D;
+    const dim3 grid(B * H * (D / kD), n);
     if (bits == 4) append_kernel<4><<<grid, kD, 0, s>>>(b, cs, H, T, n_super_cap, smin, smax);
     else append_kernel<2><<<grid, kD, 0, s>>>(b, cs, H, T, n_super_cap, smin, smax);
     return launch_status();
@@ -354,7 +366,7 @@ int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, in
     if (B * H == 0 || (T == 0 && !(tail && t_start == 0))) return 0;
     EncBatch b{};
     b.t[0] = enc_tensor(cache, x, p, tail);
-    return launch_encode(b, 1, B, H, T, n_super_cap, bits, t_start, scale_min, scale_max, stream);
+    return launch_encode(b, 1, B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max, stream);
 }
 
 int adkv_encode_kv(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *v_cache, const void *v,
@@ -369,7 +381,7 @@ int adkv_encode_kv(void *k_cache, const void *k, const adkv_params *kp, void *k_
     EncBatch b{};
     b.t[0] = enc_tensor(k_cache, k, kp, k_tail);
     b.t[1] = enc_tensor(v_cache, v, vp, v_tail);
-    return launch_encode(b, 2, B, H, T, n_super_cap, bits, t_start, scale_min, scale_max, stream);
+    return launch_encode(b, 2, B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max, stream);
 }
 
 int adkv_append(void *cache, const void *x_new, const adkv_params *p, void *tail, int B, int H, int T, int D,
@@ -380,7 +392,7 @@ int adkv_append(void *cache, const void *x_new, const adkv_params *p, void *tail
     if (B * H == 0) return 0;
     EncBatch b{};
     b.t[0] = enc_tensor(cache, x_new, p, tail);
-    return launch_append(b, 1, B, H, T, n_super_cap, bits, scale_min, scale_max, stream);
+    return launch_append(b, 1, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream);
 }
 
 int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *v_cache,
@@ -394,7 +406,7 @@ int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void
     EncBatch b{};
     b.t[0] = enc_tensor(k_cache, k_new, kp, k_tail);
     b.t[1] = enc_tensor(v_cache, v_new, vp, v_tail);
-    return launch_append(b, 2, B, H, T, n_super_cap, bits, scale_min, scale_max, stream);
+    return launch_append(b, 2, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream);
 }
 
 int adkv_encode_kv_ckpt(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
@@ -411,8 +423,8 @@ int adkv_encode_kv_ckpt(void *k_cache, const void *k, const adkv_params *kp, voi
     EncBatch b{};
     b.t[0] = enc_tensor(k_cache, k, kp, k_tail, k_ckpt);
     b.t[1] = enc_tensor(v_cache, v, vp, v_tail, v_ckpt);
-    return launch_encode(b, 2, B, H, T, n_super_cap, bits, t_start, scale_min, scale_max, stream,
-                         CkptSpec{interval, n_ckpt_cap});
+    return launch_encode(b, 2, B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max, stream,
+                         CkptSpec{interval, n_ckpt_cap, D});
 }
 
 int adkv_append_kv_ckpt(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
@@ -428,8 +440,8 @@ int adkv_append_kv_ckpt(void *k_cache, const void *k_new, const adkv_params *kp,
     EncBatch b{};
     b.t[0] = enc_tensor(k_cache, k_new, kp, k_tail, k_ckpt);
     b.t[1] = enc_tensor(v_cache, v_new, vp, v_tail, v_ckpt);
-    return launch_append(b, 2, B, H, T, n_super_cap, bits, scale_min, scale_max, stream,
-                         CkptSpec{interval, n_ckpt_cap});
+    return launch_append(b, 2, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream,
+                         CkptSpec{interval, n_ckpt_cap, D});
 }
 
 }  // extern "C"

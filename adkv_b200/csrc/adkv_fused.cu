@@ -36,13 +36,13 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
     }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mbar_init(&kbar[i], 1); mbar_init(&vbar[i], 1); }
-        for (int i = 0; i < kLogitSlots; ++i) { mbar_init(&fs.lfull[i], 1); mbar_init(&fs.lempty[i], 1); }
+        fs.init_barriers(1);
         mbar_init_fence();
     }
     __syncthreads();
-    const Seg seg{0, ka.T, true, nullptr, nullptr};
+    const Seg seg{0, ka.T, true, nullptr, nullptr, 0};
     if (warp == 0) {
-        RingSink<G> sink{&fs, 0};
+        RingSink<G> sink{&fs, 0, 0};
         k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         SoftmaxSrc<G> src;
@@ -60,6 +60,9 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
 }  // namespace adkv
 
 using namespace adkv;
+
+ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
+                                      float scaling, int B, int bits, bool exact, cudaStream_t s);
 
 // Status word of this translation unit (read and cleared by adkv_device_status).
 ADKV_HIDDEN int adkv_tu_status_fused(int *out)
@@ -86,11 +89,13 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
         return ADKV_E_ALIGN;
     if (B == 0) return 0;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    if (D != kD)
+        return adkv_wide_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, exact, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(
                       ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, nullptr)))
@@ -104,15 +109,16 @@ int adkv_decode_attn_varlen(const void *q, void *k_cache, void *v_cache, const v
 {
     if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !seq_lens || !params_ok(kp) || !params_ok(vp))
         return ADKV_E_NULL;
+    if (D != kD) return ADKV_E_HEAD_DIM;   // device-side lengths: 128-wide heads only
     if (int rc = check_common(B, Hq, Hkv, 0, D, n_super_cap, bits, 1)) return rc;
     if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
         !aligned8(v_new) || !params_aligned(kp) || !params_aligned(vp) || (reinterpret_cast<uintptr_t>(seq_lens) & 3u))
         return ADKV_E_ALIGN;
     if (B == 0) return 0;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max};
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(vp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max};
+                   to_ptrs(vp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,

@@ -36,7 +36,7 @@ static inline int launch_status()
 
 static inline int check_common(int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, int n_written_end)
 {
-    if (D != kD) return ADKV_E_HEAD_DIM;
+    if (D != 128 && D != 256 && D != 512) return ADKV_E_HEAD_DIM;
     if (bits != 2 && bits != 4) return ADKV_E_BITS;
     if (B < 0 || Hq <= 0 || Hkv <= 0 || T < 0 || n_super_cap < 0 || Hq % Hkv != 0) return ADKV_E_SHAPE;
     const int tpw = 32 / bits;

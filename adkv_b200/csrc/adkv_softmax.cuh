@@ -5,16 +5,27 @@
 
 namespace adkv {
 
-template <int G>
+// S = number of 128-channel slices of the head (head_dim / 128): each slice has its own K warp, which
+// contributes a partial logit, and its own V warp, which sums the S partials.  The full barrier of a slot
+// therefore collects S arrivals (one per K warp) and the empty barrier S arrivals (one per V warp).
+template <int G, int S = 1>
 struct FusedShared {
-    float lring[kLogitSlots][G][kTileTok];
+    float lring[kLogitSlots][S][G][kTileTok];
     uint64_t lfull[kLogitSlots], lempty[kLogitSlots];
+    __device__ __forceinline__ void init_barriers(int n_consumers)
+    {
+        for (int i = 0; i < kLogitSlots; ++i) {
+            mbar_init(&lfull[i], S);
+            mbar_init(&lempty[i], n_consumers);
+        }
+    }
 };
 
-template <int G>
+template <int G, int S = 1>
 struct RingSink {
-    FusedShared<G> *sh;
+    FusedShared<G, S> *sh;
     int slot;
+    int sl;      // this K warp's slice
     __device__ __forceinline__ bool begin_tile(int i)
     {
         slot = i % kLogitSlots;
@@ -22,20 +33,20 @@ struct RingSink {
     }
     __device__ __forceinline__ void put8(int, int g, int tok, float v, int lane)
     {
-        if (lane < 8) sh->lring[slot][g][tok + lane] = v;
+        if (lane < 8) sh->lring[slot][sl][g][tok + lane] = v;
     }
     __device__ __forceinline__ void end_tile(int, int lane)
     {
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->lfull[slot]);
     }
-    __device__ __forceinline__ void put_self(int g, float v) { sh->lring[slot][g][0] = v; }
+    __device__ __forceinline__ void put_self(int g, float v) { sh->lring[slot][sl][g][0] = v; }
     __device__ __forceinline__ void finish(int lane) { end_tile(0, lane); }
 };
 
-template <int G>
+template <int G, int S = 1>
 struct SoftmaxSrc {
-    FusedShared<G> *sh;
+    FusedShared<G, S> *sh;
     float2 *wts;           // [G][32], every weight stored twice (packed multiplier for a channel pair)
     const float *mask;     // row of this batch or nullptr
     float scale2;          // scaling * log2(e)
@@ -68,7 +79,11 @@ struct SoftmaxSrc {
         if (!mbar_wait_bounded(&sh->lfull[slot], (i / kLogitSlots) & 1, kStatLFullWait)) return false;
         float x[G];
 #pragma unroll
-        for (int g = 0; g < G; ++g) x[g] = sh->lring[slot][g][lane];
+        for (int g = 0; g < G; ++g) {
+            x[g] = sh->lring[slot][0][g][lane];
+#pragma unroll
+            for (int k = 1; k < S; ++k) x[g] += sh->lring[slot][k][g][lane];
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->lempty[slot]);
 #pragma unroll
@@ -87,7 +102,10 @@ struct SoftmaxSrc {
         const float mk = mask ? mask[T] * 1.4426950408889634f : 0.f;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const float v = fmaf(sh->lring[slot][g][0], scale2, mk);
+            float xs = sh->lring[slot][0][g][0];
+#pragma unroll
+            for (int k = 1; k < S; ++k) xs += sh->lring[slot][k][g][0];
+            const float v = fmaf(xs, scale2, mk);
             // all lanes hold the same v: update() would count it 32 times, so do it by hand
             const float m_new = fmaxf(m[g], v);
             const bool dead = (m_new == -INFINITY);
@@ -102,9 +120,9 @@ struct SoftmaxSrc {
         return true;
     }
     __device__ __forceinline__ float norm(int g) const { return l[g]; }
-    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int lane, const float (&acc)[G][4]) const
+    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int c0, const float (&acc)[G][4]) const
     {
-        store_normalised<G>(*this, a, b, h, lane, acc);
+        store_normalised<G>(*this, a, b, h, c0, acc);
     }
 };
 

@@ -19,15 +19,15 @@ constexpr int kPartStride = 4 + kD;   // floats per (stream, segment, head): max
 template <int G>
 struct PartialSrc : SoftmaxSrc<G> {
     float *part;   // [G][kPartStride] of this (stream, segment)
-    __device__ __forceinline__ void store(const VArgs &, int, int, int lane, const float (&acc)[G][4]) const
+    __device__ __forceinline__ void store(const VArgs &, int, int, int c0, const float (&acc)[G][4]) const
     {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            if (lane == 0) {
+            if (c0 == 0) {
                 part[g * kPartStride] = this->m[g];
                 part[g * kPartStride + 1] = this->l[g];
             }
-            *reinterpret_cast<float4 *>(part + g * kPartStride + 4 + 4 * lane) =
+            *reinterpret_cast<float4 *>(part + g * kPartStride + 4 + c0) =
                 make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
         }
     }
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mbar_init(&kbar[i], 1); mbar_init(&vbar[i], 1); }
-        for (int i = 0; i < kLogitSlots; ++i) { mbar_init(&fs.lfull[i], 1); mbar_init(&fs.lempty[i], 1); }
+        fs.init_barriers(1);
         mbar_init_fence();
     }
     __syncthreads();
@@ -65,13 +65,14 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
     seg.t_begin = j * ck.interval;
     seg.t_end = min(T, (j + 1) * ck.interval);
     seg.append = (j == n_seg - 1);
+    seg.slice = 0;
     const size_t stream_ckpt = size_t(bh) * ck.n_ckpt_cap;
     const bool write_ckpt = seg.append && (T + 1) % ck.interval == 0;
     const size_t out_idx = write_ckpt ? stream_ckpt + (T + 1) / ck.interval - 1 : 0;
     if (warp == 0) {
         seg.init = j ? ck.k_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
         seg.ckpt_out = write_ckpt ? ck.k_ckpt + out_idx * 2 * kD : nullptr;
-        RingSink<G> sink{&fs, 0};
+        RingSink<G> sink{&fs, 0, 0};
         k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         seg.init = j ? ck.v_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
@@ -140,6 +141,7 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
     if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !params_ok(kp) || !params_ok(vp) || !scratch ||
         !k_ckpt || !v_ckpt)
         return ADKV_E_NULL;
+    if (D != kD) return ADKV_E_HEAD_DIM;   // checkpointed decode: 128-wide heads only
     if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
     if (interval <= 0 || interval % kTileTok != 0 || n_ckpt_cap < 0) return ADKV_E_SHAPE;
     if ((T + 1) / interval > n_ckpt_cap) return ADKV_E_CAPACITY;
@@ -150,9 +152,9 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
     if (scratch_bytes < adkv_decode_attn_ckpt_scratch_bytes(B, Hq, Hkv, T, interval)) return ADKV_E_SCRATCH;
     if (B == 0) return 0;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs k
 #pragma unroll
     for (int g = 0; g < G; ++g) sink.row[g] = logits + (size_t(b) * ka.Hq + size_t(h) * G + g) * (ka.T + 1);
     sink.T = ka.T;
-    const Seg seg{0, ka.T, true, nullptr, nullptr};
+    const Seg seg{0, ka.T, true, nullptr, nullptr, 0};
     k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf[warp], kbar[warp], red[warp], sink);
 }
 
@@ -72,9 +72,9 @@ struct GlobalWeightSrc {
         return true;
     }
     __device__ __forceinline__ float norm(int) const { return 1.f; }
-    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int lane, const float (&acc)[G][4]) const
+    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int c0, const float (&acc)[G][4]) const
     {
-        store_normalised<G>(*this, a, b, h, lane, acc);
+        store_normalised<G>(*this, a, b, h, c0, acc);
     }
 };
 
@@ -98,13 +98,16 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_ov_kernel(VArgs v
 #pragma unroll
     for (int g = 0; g < G; ++g) src.row[g] = attn + (size_t(b) * va.Hq + size_t(h) * G + g) * (va.T + 1);
     src.wts = wts[warp];
-    const Seg seg{0, va.T, true, nullptr, nullptr};
+    const Seg seg{0, va.T, true, nullptr, nullptr, 0};
     v_warp<BITS, G, EXACT>(va, seg, b, h, lane, vbuf[warp], vbar[warp], wts[warp], src);
 }
 
 }  // namespace adkv
 
 using namespace adkv;
+
+ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, bool exact, cudaStream_t s);
+ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, bool exact, cudaStream_t s);
 
 // Status word of this translation unit (read and cleared by adkv_device_status).
 ADKV_HIDDEN int adkv_tu_status_unfused(int *out)
@@ -127,10 +130,11 @@ int adkv_forward_qk(const void *q, void *k_cache, const void *k_new, const adkv_
     if (!aligned16(k_cache) || !aligned8(q) || !aligned8(k_new) || !params_aligned(p)) return ADKV_E_ALIGN;
     if (B == 0) return 0;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+                   static_cast<const __half *>(k_new), to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    if (D != kD) return adkv_wide_forward_qk(ka, static_cast<__half *>(logits), B, bits, exact, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (forward_qk_kernel<BITS, G, EXACT><<<grid, 32 * kStreamsPerCta, 0, s>>>(
                       ka, static_cast<__half *>(logits), n_streams)))
@@ -146,10 +150,11 @@ int adkv_forward_ov(const void *attn, void *v_cache, const void *v_new, const ad
     if (!aligned16(v_cache) || !aligned8(out) || !aligned8(v_new) || !params_aligned(p)) return ADKV_E_ALIGN;
     if (B == 0) return 0;
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max};
+                   to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    if (D != kD) return adkv_wide_forward_ov(va, static_cast<const __half *>(attn), B, bits, exact, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (forward_ov_kernel<BITS, G, EXACT><<<grid, 32 * kStreamsPerCta, 0, s>>>(
                       va, static_cast<const __half *>(attn), n_streams)))

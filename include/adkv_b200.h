@@ -10,6 +10,8 @@
  * Return value: 0 on success, < 0 for an argument error (ADKV_E_*), > 0 for a CUDA runtime
  * error code (cudaError_t) raised by the launch.  adkv_strerror() gives text for both.
  *
+ * Head dims: D = 128, 256 or 512, as in the reference (src/adkv/hf/llama_adkv.py:97-99).
+ *
  * Packed cache layout (src/adkv/kernel/gemv.cu:502-510 for 4 bits): per (batch, kv head) a
  * row-major array uint32[n_super_cap][D]; word (sg, c) holds the codes of channel c for the
  * tokens of supergroup sg, token j of the supergroup in bits [bits*j, bits*j+bits) stored as
@@ -35,9 +37,9 @@ extern "C" {
 
 /* argument errors */
 #define ADKV_E_NULL      (-1)  /* a required pointer is NULL */
-#define ADKV_E_HEAD_DIM  (-2)  /* D is not supported (this build: 128) */
+#define ADKV_E_HEAD_DIM  (-2)  /* D is not 128, 256 or 512 (the _ckpt, _varlen and _static entry points: 128 only) */
 #define ADKV_E_BITS      (-3)  /* bits is not 2 or 4 */
-#define ADKV_E_SHAPE     (-4)  /* negative size, or Hq not a multiple of Hkv, or group size unsupported */
+#define ADKV_E_SHAPE     (-4)  /* negative size, Hq not a multiple of Hkv, or Hq/Hkv not in {1,2,4,8} ({1,2} for D > 128) */
 #define ADKV_E_CAPACITY  (-5)  /* the cache has no room for the tokens to be written */
 #define ADKV_E_ALIGN     (-6)  /* a pointer is not 16-byte aligned */
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */

@@ -88,4 +88,9 @@ def test_cache_object_errors_match_reference_behaviour():
         layer.decode(x[:, :1, :1], x[:, :1, :1], x[:, :1, :1], *p, *p)
     with pytest.raises(ValueError, match="head_dim"):
         KVCacheLayer().prefill(x[..., :64], x[..., :64], *p, *p)
+    wide = KVCacheLayer()
+    xw = torch.zeros(1, 2, 4, 256, dtype=torch.float16, device="cuda")
+    pw = _flat(synth.gen_params(0, 2, 256))
+    wide.prefill(xw, xw, *pw, *pw)                       # head_dim 256 is served (llama_adkv.py:97-99)
+    assert wide.key_states.shape == (1, 2, 8, 64, 4, 4)
     assert KVCache(3)[2].get_mask_sizes(2) == (2, 0)

@@ -408,7 +408,7 @@ def test_argument_errors_raise_runtime_error():
         gemv.forward_qk(q, cache, q, *p, -1, SMIN, SMAX)
     with pytest.raises(RuntimeError, match="k_zp must be float16"):
         gemv.forward_qk(q, cache, q, p[0].float(), *p[1:], 3, SMIN, SMAX)
-    bad = torch.zeros(1, H, 2, 64 // 4, 4, 4, dtype=torch.uint8, device="cuda")
+    bad = torch.zeros(1, H, 2, 64 // 4, 4, 4, dtype=torch.uint8, device="cuda")        # head_dim 64
     with pytest.raises(RuntimeError, match="head dim"):
         gemv.forward_qk(torch.zeros(1, H, 1, 64, dtype=torch.float16, device="cuda"), bad,
                         torch.zeros(1, H, 1, 64, dtype=torch.float16, device="cuda"),
