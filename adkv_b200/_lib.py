@@ -45,6 +45,7 @@ SIGNATURES = {
                          c_float, c_float, c_float, c_uint, c_void_p],
     "adkv_decode_attn_varlen": [c_void_p] * 9 + [c_int] * 6 + [c_float, c_float, c_float, c_uint, c_void_p],
     "adkv_device_status": [c_void_p, c_void_p],
+    "adkv_selftest_wait_timeout": [c_int, c_void_p],
 }
 _RESTYPE = {"adkv_strerror": ctypes.c_char_p, "adkv_decode_attn_ckpt_scratch_bytes": c_longlong}
 

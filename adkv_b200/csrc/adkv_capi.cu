@@ -8,6 +8,32 @@ ADKV_HIDDEN int adkv_tu_status_encode(int *out);
 ADKV_HIDDEN int adkv_tu_status_split(int *out);
 ADKV_HIDDEN int adkv_tu_status_wide(int *out);
 
+namespace adkv {
+
+// One warp waits on a barrier that nothing ever completes: the bounded wait must give up after `limit_ns`,
+// record its code in the status word and let the kernel end normally.
+__global__ void selftest_wait_kernel(unsigned long long limit_ns)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    mbar_wait_bounded(&bar, 0, kStatSelfTest, limit_ns);
+}
+
+}  // namespace adkv
+
+ADKV_HIDDEN int adkv_tu_status_capi(int *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, adkv::g_status, sizeof(int));
+    if (e != cudaSuccess) return int(e);
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(adkv::g_status, &zero, sizeof(int));
+    return e == cudaSuccess ? 0 : int(e);
+}
+
 extern "C" {
 
 int adkv_abi_version(void) { return ADKV_ABI_VERSION; }
@@ -36,14 +62,22 @@ int adkv_device_status(int *status, void *stream)
     if (!status) return ADKV_E_NULL;
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return int(e);
-    int a = 0, b = 0, c = 0, d = 0, w = 0;
+    int a = 0, b = 0, c = 0, d = 0, w = 0, t = 0;
     if (int rc = adkv_tu_status_fused(&a)) return rc;
     if (int rc = adkv_tu_status_unfused(&b)) return rc;
     if (int rc = adkv_tu_status_encode(&c)) return rc;
     if (int rc = adkv_tu_status_split(&d)) return rc;
     if (int rc = adkv_tu_status_wide(&w)) return rc;
-    *status = a ? a : (b ? b : (c ? c : (d ? d : w)));
+    if (int rc = adkv_tu_status_capi(&t)) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : (w ? w : t))));
     return 0;
+}
+
+int adkv_selftest_wait_timeout(int limit_ms, void *stream)
+{
+    if (limit_ms <= 0 || limit_ms > 2000) return ADKV_E_SHAPE;
+    adkv::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(1000000ull * (unsigned long long)limit_ms);
+    return adkv::launch_status();
 }
 
 }  // extern "C"

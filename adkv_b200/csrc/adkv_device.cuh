@@ -30,6 +30,7 @@ constexpr unsigned kFull = 0xffffffffu;
 // Status codes written to g_status when a bounded wait gives up (1-5) or an argument only the device can
 // see is unusable (6).
 constexpr int kStatKWait = 1, kStatVWait = 2, kStatLFullWait = 3, kStatLEmptyWait = 4, kStatDrain = 5;
+constexpr int kStatSelfTest = 7;   // the wait of adkv_selftest_wait_timeout ran out, as it must
 constexpr int kStatCapacity = 6;   // a device-side sequence length did not fit the cache: that stream was skipped
 
 // One status word per translation unit that includes this header (the library is one unit).
@@ -389,7 +390,8 @@ __device__ __forceinline__ uint64_t globaltimer_ns()
 // the result is warp-uniform.  On failure the status word records `code`.  A warp that finds the
 // phase incomplete sleeps between polls so that it does not take issue slots from the warps it is
 // waiting for.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int code)
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int code,
+                                                  uint64_t limit_ns = 1000000000ull)
 {
     bool ok = mbar_try_wait(bar, parity);
     if (!ok) {
@@ -398,7 +400,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
             __nanosleep(it < 8 ? 128 : 512);
             ok = mbar_try_wait(bar, parity);
             if (ok) break;
-            if ((it & 63u) == 0 && globaltimer_ns() - t0 > 1000000000ull) break;
+            if ((it & 63u) == 0 && globaltimer_ns() - t0 > limit_ns) break;
         }
     }
     ok = __all_sync(kFull, ok);

@@ -191,6 +191,12 @@ int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, co
  * stream whose device-side length did not fit the cache (6).  Intended for tests and diagnostics, not for the hot path. */
 int adkv_device_status(int *status, void *stream);
 
+/* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits on a barrier
+ * nothing will ever complete.  The wait gives up after limit_ms (1..2000), the kernel ends normally, and
+ * adkv_device_status then reports 7.  Every wait in the library's kernels uses the same routine with a 1 s
+ * limit, so a lost copy or a missing partner ends as a status code, not as a hang. */
+int adkv_selftest_wait_timeout(int limit_ms, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

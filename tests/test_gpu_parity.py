@@ -386,6 +386,24 @@ def test_full_size_config3_prefill_properties(bits):
     assert torch.equal(parts, one) and torch.equal(t_parts.view(torch.int32), t_one.view(torch.int32))
 
 
+def test_bounded_wait_gives_up_and_reports():
+    """A wait that nothing completes must end after its limit with a status code; the context stays usable."""
+    import ctypes
+    import time
+    from adkv_b200 import _lib
+    assert gemv.device_status() == 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    t0 = time.perf_counter()
+    _lib.check(_lib.load().adkv_selftest_wait_timeout(50, stream), "selftest")
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert 0.04 < dt < 1.0, dt
+    assert gemv.device_status() == 7
+    assert gemv.device_status() == 0                                   # reading clears it
+    x = torch.arange(8, device="cuda")
+    assert int((x * 2).sum()) == 56                                    # the device still answers
+
+
 # ------------------------------------------------------------------------------- errors
 
 def test_argument_errors_raise_runtime_error():
