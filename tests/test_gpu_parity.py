@@ -248,6 +248,38 @@ def test_decode_varlen_ragged_batch(bits, Hq, Hkv):
     assert torch.equal(kc[2], before[2])
 
 
+def test_decode_with_infinite_mask_entries():
+    """-inf mask entries (whole leading tiles masked, and a fully masked cache for one sequence) give the same
+    result as dropping those tokens; no NaN from the online softmax."""
+    B, H, T, bits, D = 2, 2, 100, 4, 128
+    case = make_case(660, B, H, H, T, bits)
+    kc, vc = oracle_prefill(case)
+    mask = torch.zeros(B, T + 1)
+    mask[0, :70] = float("-inf")                # two whole 32-token tiles and part of a third
+    mask[1, :T] = float("-inf")                 # everything but the token being appended
+    wk, wv = kc.copy(), vc.copy()
+    want = orc.decode_attn(case["q"][:, :, 0].numpy(), wk, wv, case["k"][:, :, T].numpy(), case["v"][:, :, T].numpy(),
+                           np_params(case["kp"]), np_params(case["vp"]), T, 0.1, mask=mask[:, None].numpy(), bits=bits,
+                           scale_min=SMIN, scale_max=SMAX)
+    assert np.isfinite(want).all()
+    for kw in ({}, {"ckpt": True}):
+        dk, dv = dev(kc), dev(vc)
+        extra = {}
+        if kw:
+            kck, vck = gemv.alloc_ckpt(B, H, D, T + 1, 32, "cuda"), gemv.alloc_ckpt(B, H, D, T + 1, 32, "cuda")
+            fk, fv = torch.zeros_like(dk), torch.zeros_like(dv)
+            gemv.encode_kv_pair(fk, dev(case["k"][:, :, :T]), dev(case["kp"]), fv, dev(case["v"][:, :, :T]),
+                                dev(case["vp"]), SMIN, SMAX, bits=bits, k_ckpt=kck, v_ckpt=vck, ckpt_interval=32)
+            assert torch.equal(fk, dk) and torch.equal(fv, dv)
+            extra = dict(k_ckpt=kck, v_ckpt=vck, ckpt_interval=32)
+        got = gemv.decode_attn(dev(case["q"]), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
+                               dev(case["kp"]), dev(case["vp"]), T, 0.1, SMIN, SMAX, mask=dev(mask), bits=bits, **extra)
+        _status_ok()
+        g = got.float().cpu().numpy()
+        assert np.isfinite(g).all()
+        np.testing.assert_allclose(g, want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+
+
 def test_decode_steps_chain_like_generation():
     """Prefill with the kernel, then 40 fused decode steps; caches stay bit-identical to the oracle's."""
     B, H, T0, steps, bits, D = 2, 2, 21, 40, 4, 128
