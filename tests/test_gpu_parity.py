@@ -387,6 +387,16 @@ def test_full_size_config5_gqa_2bit_properties():
     np.testing.assert_allclose(got[:1], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
     assert np.array_equal(dk[:1].cpu().numpy(), kc) and np.array_equal(dv[-1:].cpu().numpy(), vc)
     assert torch.equal(dk[0], dk[-1]) and torch.equal(dv[0], dv[-1])
+    # contracted replay over 32768 tokens: output within tolerance, appended codes within the 1e-4 allowance
+    out_f = gemv.decode_attn(rep(case["q"]), dk, dv, rep(case["k"][:, :, T:T + 1]), rep(case["v"][:, :, T:T + 1]),
+                             dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits, fast=True)
+    _status_ok()
+    np.testing.assert_allclose(out_f.float().cpu().numpy()[:1], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    for got_c, want_c in ((dk[:1].cpu().numpy(), kc), (dv[:1].cpu().numpy(), vc)):
+        a = orc.unpack_codes(got_c, T + 1, bits)[:, :, T].astype(np.int32)
+        b = orc.unpack_codes(want_c, T + 1, bits)[:, :, T].astype(np.int32)
+        d = np.abs(a - b)
+        assert d.max() <= 1 and (d != 0).mean() <= 1e-4 + 1.5 / d.size, ((d != 0).sum(), d.size)
 
 
 @pytest.mark.parametrize("bits", [4, 2])
