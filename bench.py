@@ -16,8 +16,11 @@ runs the same per-GPU batch on its own shard of sequences (no data-path collecti
              HBM copy bandwidth of MEASURED_PEAKS.json.
 ``cpu_baseline``: the C restatement of the reference algorithm (oracle/) on the host cores, on a
              bounded sample of the same workload; also used to check the GPU result of the sample.
-``--impl reference`` times that CPU implementation alone (the reference's CUDA file needs its own
-torch extension build and computes in fp16, and its torch path cannot travel to the GPU box).
+``--impl reference`` times that CPU implementation alone (the reference's torch path cannot travel to
+             the GPU box).
+``reference_cuda``, ``unfused_trio``: for the record, the reference caller's three-call sequence
+             (forward_qk, torch softmax, forward_ov) through the reference's own CUDA kernels recompiled for
+             sm_100a (oracle/_ref, when built; they compute in fp16) and through this library's kernels.
 """
 from __future__ import annotations
 
@@ -304,6 +307,32 @@ def check_against_oracle(w, st, out, n_streams, torch):
     return ok, dt, n_streams, c_oracle.num_threads()
 
 
+def time_cuda(fn, torch, device, steps, warmup=3):
+    """Average milliseconds per call of ``fn`` (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) / steps
+
+
+def reference_cuda_module(w):
+    """The reference's own CUDA extension (built by oracle/build_ref.py) when it exists and covers the workload:
+    4-bit codes, as many query heads as KV heads (src/adkv/hf/llama_adkv.py:235-238)."""
+    if w["bits"] != 4 or w["Hq"] != w["Hkv"]:
+        return None
+    try:
+        from oracle import ref_cuda
+        return ref_cuda.module()
+    except Exception:
+        return None
+
+
 def run_encode(args, w, name):
     """Prefill-quantise workload: a step encodes one layer's K and V (one launch of encode_kernel over both)."""
     import numpy as np
@@ -396,6 +425,20 @@ def run_encode(args, w, name):
     ok = np.array_equal(kc[:nb, :, :used].cpu().numpy(), kc_cpu[:, :, :used])
 
     nbytes = algorithmic_bytes(w)
+    ref_cuda_leg = None
+    ref = reference_cuda_module(w)
+    if ref is not None:
+        # the reference's encode kernel (fp16 state), one call per tensor as its caller makes them
+        rk, rv = torch.zeros_like(kc), torch.zeros_like(vc)
+
+        def ref_step():
+            ref.encode_kv(rk, k, *kp, synth.SCALE_MIN, synth.SCALE_MAX)
+            ref.encode_kv(rv, v, *vp, synth.SCALE_MIN, synth.SCALE_MAX)
+        ms = time_cuda(ref_step, torch, device, max(1, min(args.steps, 10)), warmup=2)
+        ref_cuda_leg = {"ms_per_step": ms, "value": nbytes / (ms * 1e-3) / 1e9, "unit": UNIT,
+                        "what": "the reference's encode_kv CUDA kernel (fp16 state) recompiled for sm_100a, K then V, "
+                                "same tensors resident in HBM"}
+        del rk, rv
     peak, peak_src = measured_peak_gbs()
     avg_ms = sum(per_step) / len(per_step)
     res = {
@@ -417,6 +460,8 @@ def run_encode(args, w, name):
                          "sample": f"K of {nb} of {B} sequences ({nb * H} streams), C restatement with OpenMP"},
         "parity_check": "ok" if ok else "FAILED",
     }
+    if ref_cuda_leg:
+        res["reference_cuda"] = ref_cuda_leg
     print(json.dumps(res), flush=True)
     if not ok:
         sys.exit(1)
@@ -515,6 +560,30 @@ def run_ours(args, w, name):
     o1.record()
     barrier()
     other_ms = o0.elapsed_time(o1) / other_steps
+    # the three-call sequence of the reference's caller (src/adkv/hf/llama_adkv.py:263-276): unscaled logits,
+    # torch softmax in fp32, weighted sum -- through this library's kernels and, where it has been built and
+    # covers the workload, through the reference's own CUDA kernels recompiled for sm_100a
+    trio_legs = {}
+    if world == 1 and not args.ckpt_interval:
+        def trio(qk, ov, **kw):
+            def fn():
+                logits = qk(st["q"], kc2, st["kn"], *st["kp"], T, synth.SCALE_MIN, synth.SCALE_MAX, **kw)
+                attn = torch.softmax(logits.float() * scaling, dim=-1).to(torch.float16)
+                return ov(attn, vc2, st["vn"], *st["vp"], synth.SCALE_MIN, synth.SCALE_MAX, **kw)
+            return fn
+        kc2, vc2 = st["kc"].clone(), st["vc"].clone()
+        n_trio = max(1, min(args.steps, 20))
+        ms = time_cuda(trio(gemv.forward_qk, gemv.forward_ov, bits=bits, fast=fast), torch, device, n_trio)
+        trio_legs["unfused_trio"] = {"ms_per_step": ms, "value": algorithmic_bytes(w) / (ms * 1e-3) / 1e9, "unit": UNIT,
+                                     "what": "forward_qk + torch softmax + forward_ov of this library"}
+        ref = reference_cuda_module(w)
+        if ref is not None:
+            ms = time_cuda(trio(ref.forward_qk, ref.forward_ov), torch, device, n_trio)
+            trio_legs["reference_cuda"] = {
+                "ms_per_step": ms, "value": algorithmic_bytes(w) / (ms * 1e-3) / 1e9, "unit": UNIT,
+                "what": "the reference's forward_qk + torch softmax + forward_ov, its CUDA kernels (fp16 state and "
+                        "accumulation) recompiled for sm_100a, same caches resident in HBM"}
+        del kc2, vc2
     step()                      # leave the caches and `out` as the headline arithmetic writes them
     torch.cuda.synchronize(device)
 
@@ -554,6 +623,7 @@ def run_ours(args, w, name):
             "other_replay": {"replay": "fast" if other else "exact", "ms_per_step": other_ms,
                              "value": bytes_rank * world / (other_ms * 1e-3) / 1e9, "unit": UNIT},
         }
+        res.update(trio_legs)
         if world == 1 and not args.no_cpu:
             n = pick_sample_streams(w, target_s=args.cpu_seconds)
             ok, dt, n_used, cores = check_against_oracle(w, st, out, n, torch)
