@@ -14,6 +14,11 @@ c_void_p, c_int, c_float, c_uint, c_longlong = (ctypes.c_void_p, ctypes.c_int, c
                                                  ctypes.c_uint, ctypes.c_longlong)
 
 FLAG_FAST_REPLAY = 1
+FLAG_HALF_STATE = 2
+
+
+def flags(fast: bool = False, half_state: bool = False) -> int:
+    return (FLAG_FAST_REPLAY if fast else 0) | (FLAG_HALF_STATE if half_state else 0)
 
 # name -> argument types (return type is int unless listed in _RESTYPE); mirrors include/adkv_b200.h
 SIGNATURES = {
@@ -25,6 +30,8 @@ SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "adkv_append_kv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "adkv_encode_kv_flags": [c_void_p] * 8 + [c_int] * 7 + [c_float, c_float, c_uint, c_void_p],
+    "adkv_append_kv_flags": [c_void_p] * 8 + [c_int] * 6 + [c_float, c_float, c_uint, c_void_p],
     "adkv_encode_kv_ckpt": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_void_p],
     "adkv_append_kv_ckpt": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_void_p],
     "adkv_decode_attn_ckpt_scratch_bytes": [c_int, c_int, c_int, c_int, c_int],

@@ -12,6 +12,8 @@ from token 0, decode one token at a time), on top of the B200 kernels.  Differen
 * grouped-query attention (more query heads than KV heads), which the reference rejects
   (``llama_adkv.py:235-238``);
 * ``bits`` = 4 (reference layout) or 2;
+* ``half_state=True``: the fp16-state arithmetic of the reference's own CUDA kernels (``src/adkv/kernel/gemv.cu:150-164``)
+  instead of the fp32 definition, so that the buffers can be exchanged with caches those kernels wrote;
 * ``checkpoint_interval`` (with ``capacity_tokens``): keep recurrence-state checkpoints every that many tokens
   and decode with one warp pair per segment instead of one per sequence (long contexts, small batches).
 """
@@ -28,12 +30,14 @@ CAP_LEN = 64        # src/adkv/hf/llama_adkv.py:41
 
 class KVCacheLayer:
     def __init__(self, bits: int = 4, fused: bool = True, fast: bool = False, capacity_tokens: int | None = None,
-                 checkpoint_interval: int = 0):
+                 checkpoint_interval: int = 0, half_state: bool = False):
         if bits not in (2, 4):
             raise ValueError("bits must be 2 or 4")
         if checkpoint_interval and (not capacity_tokens or not fused or checkpoint_interval % 32):
             raise ValueError("checkpoints need a fused cache with capacity_tokens and an interval that is a multiple of 32")
-        self.bits, self.fused, self.fast = bits, fused, fast
+        if half_state and checkpoint_interval:
+            raise ValueError("state checkpoints belong to the fp32 recurrence (no half_state)")
+        self.bits, self.fused, self.fast, self.half_state = bits, fused, fast, half_state
         self._ckpt_interval = checkpoint_interval
         self._kck = self._vck = None
         self._tpw = 32 // bits
@@ -127,7 +131,8 @@ class KVCacheLayer:
                             (v(key_zp_init), v(key_scale_init), v(key_alpha), v(key_beta), v(key_quant_target)),
                             self._value_buf, value,
                             (v(value_zp_init), v(value_scale_init), v(value_alpha), v(value_beta),
-                             v(value_quant_target)), SCALE_MIN, SCALE_MAX, bits=self.bits, **self._ckpt_kwargs())
+                             v(value_quant_target)), SCALE_MIN, SCALE_MAX, bits=self.bits,
+                            half_state=self.half_state, **self._ckpt_kwargs())
         self._quant_len += T
 
     # ------------------------------------------------------------------ decode
@@ -165,17 +170,17 @@ class KVCacheLayer:
         if self.fused and (mask is None or mask.numel() == B * (ctx_len + 1)):
             out = gemv.decode_attn(q, self._key_buf, self._value_buf, k, v, kp, vp, ctx_len, scaling,
                                    SCALE_MIN, SCALE_MAX, mask=mask, bits=self.bits, fast=self.fast,
-                                   **self._ckpt_kwargs())
+                                   half_state=self.half_state, **self._ckpt_kwargs())
             weights = None
         else:
             logits = gemv.forward_qk(q, self._key_buf, k, *kp, ctx_len, SCALE_MIN, SCALE_MAX,
-                                     bits=self.bits, fast=self.fast)
+                                     bits=self.bits, fast=self.fast, half_state=self.half_state)
             logits = logits.float() * scaling
             if mask is not None:
                 logits = logits + mask.float()
             weights = torch.softmax(logits, dim=-1).to(torch.float16)
             out = gemv.forward_ov(weights, self._value_buf, v, *vp, SCALE_MIN, SCALE_MAX,
-                                  bits=self.bits, fast=self.fast)
+                                  bits=self.bits, fast=self.fast, half_state=self.half_state)
         self._quant_len = ctx_len + 1
         return out.to(query_states.dtype), weights
 

@@ -7,6 +7,7 @@ ADKV_HIDDEN int adkv_tu_status_unfused(int *out);
 ADKV_HIDDEN int adkv_tu_status_encode(int *out);
 ADKV_HIDDEN int adkv_tu_status_split(int *out);
 ADKV_HIDDEN int adkv_tu_status_wide(int *out);
+ADKV_HIDDEN int adkv_tu_status_half(int *out);
 
 namespace adkv {
 
@@ -50,6 +51,7 @@ const char *adkv_strerror(int code)
     case ADKV_E_ALIGN: return "adkv: pointer not sufficiently aligned (cache 16 bytes, fp16 rows 8 bytes)";
     case ADKV_E_START: return "adkv: t_start > 0 needs a tail state";
     case ADKV_E_SCRATCH: return "adkv: scratch memory too small for this problem";
+    case ADKV_E_FLAGS: return "adkv: ADKV_FLAG_HALF_STATE is not available for this entry point or head dim (checkpointed decode; decode with head dims 256/512)";
     case ADKV_E_STATIC_MAX:
         return "adkv: problem needs more than the 16 MiB of built-in scratch (ADKV_STATIC_SCRATCH_BYTES); use "
                "adkv_decode_attn_ckpt with caller-owned scratch, or a larger checkpoint interval";
@@ -62,14 +64,15 @@ int adkv_device_status(int *status, void *stream)
     if (!status) return ADKV_E_NULL;
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return int(e);
-    int a = 0, b = 0, c = 0, d = 0, w = 0, t = 0;
+    int a = 0, b = 0, c = 0, d = 0, w = 0, t = 0, hf = 0;
     if (int rc = adkv_tu_status_fused(&a)) return rc;
     if (int rc = adkv_tu_status_unfused(&b)) return rc;
     if (int rc = adkv_tu_status_encode(&c)) return rc;
     if (int rc = adkv_tu_status_split(&d)) return rc;
     if (int rc = adkv_tu_status_wide(&w)) return rc;
     if (int rc = adkv_tu_status_capi(&t)) return rc;
-    *status = a ? a : (b ? b : (c ? c : (d ? d : (w ? w : t))));
+    if (int rc = adkv_tu_status_half(&hf)) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : (w ? w : (hf ? hf : t)))));
     return 0;
 }
 

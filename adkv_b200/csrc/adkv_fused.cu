@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
 
 using namespace adkv;
 
+ADKV_HIDDEN int adkv_half_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
+                                      float scaling, int B, int bits, const int *seq_lens, cudaStream_t s);
 ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
                                       float scaling, int B, int bits, bool exact, cudaStream_t s);
 
@@ -93,6 +95,8 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
                    to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & ADKV_FLAG_HALF_STATE)
+        return adkv_half_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, nullptr, s);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     if (D != kD)
         return adkv_wide_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, exact, s);
@@ -120,6 +124,8 @@ int adkv_decode_attn_varlen(const void *q, void *k_cache, void *v_cache, const v
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
                    to_ptrs(vp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & ADKV_FLAG_HALF_STATE)
+        return adkv_half_decode_attn(ka, va, nullptr, 0, scaling, B, bits, static_cast<const int *>(seq_lens), s);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(ka, va, nullptr, 0, scaling,

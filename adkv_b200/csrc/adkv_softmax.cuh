@@ -44,7 +44,20 @@ struct RingSink {
     __device__ __forceinline__ void finish(int lane) { end_tile(0, lane); }
 };
 
-template <int G, int S = 1>
+// Weights of a tile for the V warp: [G][32] float2 (w, w), or with HALF_W [G][32] fp16 pairs (w, w) in the first
+// half of the same array (the fp16-state kernels multiply in fp16x2).
+template <bool HALF_W>
+__device__ __forceinline__ void put_weight(float2 *wts, int idx, float w)
+{
+    if (HALF_W) {
+        const __half2 h = __floats2half2_rn(w, w);
+        reinterpret_cast<uint32_t *>(wts)[idx] = *reinterpret_cast<const uint32_t *>(&h);
+    } else {
+        wts[idx] = make_float2(w, w);
+    }
+}
+
+template <int G, int S = 1, bool HALF_W = false>
 struct SoftmaxSrc {
     FusedShared<G, S> *sh;
     float2 *wts;           // [G][32], every weight stored twice (packed multiplier for a channel pair)
@@ -90,7 +103,7 @@ struct SoftmaxSrc {
         for (int g = 0; g < G; ++g) {
             const float v = lane < ntok ? fmaf(x[g], scale2, mk) : -INFINITY;
             const float pw = update(g, v, acc);
-            wts[g * kTileTok + lane] = make_float2(pw, pw);
+            put_weight<HALF_W>(wts, g * kTileTok + lane, pw);
         }
         __syncwarp();
         return true;

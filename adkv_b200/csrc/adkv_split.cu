@@ -157,6 +157,7 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
                    to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & ADKV_FLAG_HALF_STATE) return ADKV_E_FLAGS;   // checkpoints hold fp32 states of the fp32 recurrence
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     const int n_seg = T / interval + 1;
     if (n_seg > 65535) return ADKV_E_SHAPE;

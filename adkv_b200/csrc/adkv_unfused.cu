@@ -2,29 +2,12 @@
 // and the reference interface each one replaces.
 #include "adkv_host.h"
 
-#include "adkv_decode.cuh"
+#include "adkv_io.cuh"
 
 namespace adkv {
 
 // =========================================================================================
 // Unfused entry points (the reference's two-kernel decode): 2 streams per CTA, one warp each.
-
-constexpr int kStreamsPerCta = 2;
-
-template <int G>
-struct GlobalLogitSink {
-    __half *row[G];   // logits row of each q head of this stream: [T+1]
-    int T;
-    __device__ __forceinline__ bool begin_tile(int) { return true; }
-    __device__ __forceinline__ void put8(int i, int g, int tok, float v, int lane)
-    {
-        const int t = i * kTileTok + tok + lane;
-        if (lane < 8 && t < T) row[g][t] = __float2half_rn(v);
-    }
-    __device__ __forceinline__ void end_tile(int, int) {}
-    __device__ __forceinline__ void put_self(int g, float v) { row[g][T] = __float2half_rn(v); }
-    __device__ __forceinline__ void finish(int) {}
-};
 
 template <int BITS, int G, bool EXACT>
 __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs ka, __half *__restrict__ logits,
@@ -49,34 +32,6 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_qk_kernel(KArgs k
     const Seg seg{0, ka.T, true, nullptr, nullptr, 0};
     k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf[warp], kbar[warp], red[warp], sink);
 }
-
-template <int G>
-struct GlobalWeightSrc {
-    const __half *row[G];   // attention weights of each q head of this stream: [T+1]
-    float2 *wts;   // every weight stored twice
-    __device__ __forceinline__ bool tile_weights(int i, int ntok, int lane, float (&)[G][4])
-    {
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-        {
-            const float wv = lane < ntok ? __half2float(row[g][i * kTileTok + lane]) : 0.f;
-            wts[g * kTileTok + lane] = make_float2(wv, wv);
-        }
-        __syncwarp();
-        return true;
-    }
-    __device__ __forceinline__ bool self_weight(int, float (&)[G][4], float (&w_self)[G], int T)
-    {
-#pragma unroll
-        for (int g = 0; g < G; ++g) w_self[g] = __half2float(row[g][T]);
-        return true;
-    }
-    __device__ __forceinline__ float norm(int) const { return 1.f; }
-    __device__ __forceinline__ void store(const VArgs &a, int b, int h, int c0, const float (&acc)[G][4]) const
-    {
-        store_normalised<G>(*this, a, b, h, c0, acc);
-    }
-};
 
 template <int BITS, int G, bool EXACT>
 __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_ov_kernel(VArgs va, const __half *__restrict__ attn,
@@ -106,6 +61,8 @@ __global__ void __launch_bounds__(32 * kStreamsPerCta) forward_ov_kernel(VArgs v
 
 using namespace adkv;
 
+ADKV_HIDDEN int adkv_half_forward_qk(const KArgs &ka, __half *logits, int B, int bits, cudaStream_t s);
+ADKV_HIDDEN int adkv_half_forward_ov(const VArgs &va, const __half *attn, int B, int bits, cudaStream_t s);
 ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, bool exact, cudaStream_t s);
 ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, bool exact, cudaStream_t s);
 
@@ -133,6 +90,7 @@ int adkv_forward_qk(const void *q, void *k_cache, const void *k_new, const adkv_
                    static_cast<const __half *>(k_new), to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & ADKV_FLAG_HALF_STATE) return adkv_half_forward_qk(ka, static_cast<__half *>(logits), B, bits, s);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     if (D != kD) return adkv_wide_forward_qk(ka, static_cast<__half *>(logits), B, bits, exact, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
@@ -153,6 +111,7 @@ int adkv_forward_ov(const void *attn, void *v_cache, const void *v_new, const ad
                    to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & ADKV_FLAG_HALF_STATE) return adkv_half_forward_ov(va, static_cast<const __half *>(attn), B, bits, s);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     if (D != kD) return adkv_wide_forward_ov(va, static_cast<const __half *>(attn), B, bits, exact, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,

@@ -62,12 +62,14 @@ def _cache_dims(cache: torch.Tensor, name: str):
 
 
 def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min, scale_max, *,
-              bits: int = 4, tail: torch.Tensor | None = None, t_start: int = 0):
+              bits: int = 4, tail: torch.Tensor | None = None, t_start: int = 0, half_state: bool = False):
     """Prefill: quantise tokens ``[t_start, t_start+T)`` into the packed cache, in place.
 
     Same contract as the reference's ``encode_kv`` (``src/adkv/kernel/gemv.py:100-132``) for
     ``t_start == 0``.  ``tail`` (float32 ``[B, nh, 2, DIM]``) optionally receives the state after the
-    last token and, for ``t_start > 0``, supplies the state to continue from.  Returns ``kv_cache``."""
+    last token and, for ``t_start > 0``, supplies the state to continue from.  ``half_state`` selects the
+    arithmetic of the reference's CUDA kernels (fp16 state: codes equal to theirs bit for bit) instead of the
+    fp32 definition.  Returns ``kv_cache``."""
     _require(kv_new.dtype == torch.float16, "kv_new must be float16")
     B, H, n_super_cap, D = _cache_dims(kv_cache, "kv_cache")
     _require(kv_cache.is_contiguous(), "kv_cache must be contiguous (written in place)")
@@ -85,9 +87,15 @@ def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min
         _require(tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape == (B, H, 2, D),
                  "tail must be contiguous float32 [B, nh, 2, DIM]")
     with torch.cuda.device(kv_cache.device):
-        rc = _lib.load().adkv_encode(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
-                                     None if tail is None else tail.data_ptr(), B, H, T, D, n_super_cap, bits,
-                                     t_start, scale_min, scale_max, _stream(kv_cache))
+        if half_state:
+            rc = _lib.load().adkv_encode_kv_flags(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
+                                                  None if tail is None else tail.data_ptr(), None, None, None, None,
+                                                  B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max,
+                                                  _lib.FLAG_HALF_STATE, _stream(kv_cache))
+        else:
+            rc = _lib.load().adkv_encode(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
+                                         None if tail is None else tail.data_ptr(), B, H, T, D, n_super_cap, bits,
+                                         t_start, scale_min, scale_max, _stream(kv_cache))
     _lib.check(rc, "encode_kv")
     return kv_cache
 
@@ -122,7 +130,8 @@ def _tail_ptr(tail, B, H, D):
 
 
 def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min, scale_max, *, bits: int = 4,
-                   k_tail=None, v_tail=None, t_start: int = 0, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0):
+                   k_tail=None, v_tail=None, t_start: int = 0, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0,
+                   half_state: bool = False):
     """``encode_kv`` for the K and V tensors of one layer in a single launch (same contract each;
     replaces the two calls of ``src/adkv/hf/llama_adkv.py:144-153``).  With ``k_ckpt`` / ``v_ckpt`` /
     ``ckpt_interval`` every state checkpoint reached is written as well (see :func:`alloc_ckpt`)."""
@@ -142,8 +151,15 @@ def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min
     kp, keep_k = _params(names, tuple(k_params), H, D, k_cache.device)
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
+    _require(not (half_state and ckpt_interval), "state checkpoints belong to the fp32 recurrence (no half_state)")
     with torch.cuda.device(k_cache.device):
-        if ckpt_interval:
+        if half_state:
+            rc = _lib.load().adkv_encode_kv_flags(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                                  _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
+                                                  ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D,
+                                                  n_super_cap, bits, t_start, scale_min, scale_max,
+                                                  _lib.FLAG_HALF_STATE, _stream(k_cache))
+        elif ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D)
             rc = _lib.load().adkv_encode_kv_ckpt(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
                                                  _tail_ptr(k_tail, B, H, D), kc, v_cache.data_ptr(), xv.data_ptr(),
@@ -160,7 +176,7 @@ def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min
 
 
 def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v_tail, T: int, scale_min, scale_max,
-                   *, bits: int = 4, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0):
+                   *, bits: int = 4, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0, half_state: bool = False):
     """``append_kv`` for K and V of one layer in a single launch (optionally maintaining state checkpoints)."""
     B, H, n_super_cap, D = _cache_dims(k_cache, "cache")
     _require(tuple(v_cache.shape) == tuple(k_cache.shape) and v_cache.dtype == torch.uint8 and v_cache.is_cuda,
@@ -175,8 +191,15 @@ def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v
     kp, keep_k = _params(names, tuple(k_params), H, D, k_cache.device)
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
+    _require(not (half_state and ckpt_interval), "state checkpoints belong to the fp32 recurrence (no half_state)")
     with torch.cuda.device(k_cache.device):
-        if ckpt_interval:
+        if half_state:
+            rc = _lib.load().adkv_append_kv_flags(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
+                                                  _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
+                                                  ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D,
+                                                  n_super_cap, bits, scale_min, scale_max, _lib.FLAG_HALF_STATE,
+                                                  _stream(k_cache))
+        elif ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D)
             rc = _lib.load().adkv_append_kv_ckpt(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
                                                  _tail_ptr(k_tail, B, H, D), kc, v_cache.data_ptr(), xv.data_ptr(),
@@ -192,7 +215,8 @@ def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v
     return k_cache, v_cache
 
 
-def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min, scale_max, *, bits: int = 4):
+def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min, scale_max, *, bits: int = 4,
+              half_state: bool = False):
     """Quantise ``x_new [B, nh, 1, DIM]`` with the persisted ``tail`` state (after token ``T-1``),
     write it as token ``T`` and advance ``tail`` in place.  Returns ``cache``."""
     B, H, n_super_cap, D = _cache_dims(cache, "cache")
@@ -206,14 +230,19 @@ def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min
     p, keep = _params(("zp", "sc", "alpha", "beta", "target"), (zp, sc, alpha, beta, target), H, D, cache.device)
     x = x_new.contiguous()
     with torch.cuda.device(cache.device):
-        rc = _lib.load().adkv_append(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
-                                     B, H, T, D, n_super_cap, bits, scale_min, scale_max, _stream(cache))
+        if half_state:
+            rc = _lib.load().adkv_append_kv_flags(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
+                                                  None, None, None, None, B, H, T, D, n_super_cap, bits, scale_min,
+                                                  scale_max, _lib.FLAG_HALF_STATE, _stream(cache))
+        else:
+            rc = _lib.load().adkv_append(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
+                                         B, H, T, D, n_super_cap, bits, scale_min, scale_max, _stream(cache))
     _lib.check(rc, "append_kv")
     return cache
 
 
 def forward_qk(q, k_cache, k_new, k_zp, k_sc, k_alpha, k_beta, k_t, T: int, scale_min, scale_max, *,
-               bits: int = 4, fast: bool = False):
+               bits: int = 4, fast: bool = False, half_state: bool = False):
     """Decode-phase q.K^T over the packed cache; appends ``k_new`` as token ``T`` in place.
 
     Same contract as the reference's ``forward_qk`` (``src/adkv/kernel/gemv.py:16-55``): returns
@@ -238,13 +267,13 @@ def forward_qk(q, k_cache, k_new, k_zp, k_sc, k_alpha, k_beta, k_t, T: int, scal
     with torch.cuda.device(k_cache.device):
         rc = _lib.load().adkv_forward_qk(qc.data_ptr(), k_cache.data_ptr(), kn.data_ptr(), ctypes.addressof(p),
                                          o.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scale_min, scale_max,
-                                         _lib.FLAG_FAST_REPLAY if fast else 0, _stream(k_cache))
+                                         _lib.flags(fast, half_state), _stream(k_cache))
     _lib.check(rc, "forward_qk")
     return o
 
 
 def forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min, scale_max, *,
-               bits: int = 4, fast: bool = False):
+               bits: int = 4, fast: bool = False, half_state: bool = False):
     """Decode-phase P.V over the packed cache; appends ``v_new`` as token ``T = attn.shape[2] - 1``.
 
     Same contract as the reference's ``forward_ov`` (``src/adkv/kernel/gemv.py:58-97``): returns
@@ -268,7 +297,7 @@ def forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min
     with torch.cuda.device(v_cache.device):
         rc = _lib.load().adkv_forward_ov(ac.data_ptr(), v_cache.data_ptr(), vn.data_ptr(), ctypes.addressof(p),
                                          o.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scale_min, scale_max,
-                                         _lib.FLAG_FAST_REPLAY if fast else 0, _stream(v_cache))
+                                         _lib.flags(fast, half_state), _stream(v_cache))
     _lib.check(rc, "forward_ov")
     return o
 
@@ -282,7 +311,7 @@ def decode_scratch_bytes(B: int, Hq: int, Hkv: int, T: int, interval: int) -> in
 
 def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
                 scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False,
-                out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0,
+                half_state: bool = False, out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0,
                 scratch: torch.Tensor | None = None):
     """Fused decode step over both packed caches.
 
@@ -322,7 +351,7 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
     else:
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
-    flags = _lib.FLAG_FAST_REPLAY if fast else 0
+    flags = _lib.flags(fast, half_state)
     with torch.cuda.device(k_cache.device):
         if ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, Hkv, D)
@@ -347,7 +376,8 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
 
 
 def decode_attn_varlen(q, k_cache, v_cache, k_new, v_new, k_params, v_params, seq_lens, scaling: float,
-                       scale_min, scale_max, *, bits: int = 4, fast: bool = False, out: torch.Tensor | None = None):
+                       scale_min, scale_max, *, bits: int = 4, fast: bool = False, half_state: bool = False,
+                       out: torch.Tensor | None = None):
     """Fused decode step with per-sequence lengths on the device.
 
     ``seq_lens`` int32 ``[B]`` CUDA tensor: sequence ``b`` attends over its ``seq_lens[b]`` cached tokens and
@@ -380,7 +410,7 @@ def decode_attn_varlen(q, k_cache, v_cache, k_new, v_new, k_params, v_params, se
                                                  vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp),
                                                  seq_lens.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, n_super_cap,
                                                  bits, scaling, scale_min, scale_max,
-                                                 _lib.FLAG_FAST_REPLAY if fast else 0, _stream(k_cache))
+                                                 _lib.flags(fast, half_state), _stream(k_cache))
     _lib.check(rc, "decode_attn_varlen")
     return out
 
@@ -390,7 +420,7 @@ STATIC_SCRATCH_BYTES = 16 << 20
 
 def decode_attn_static(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
                        scale_min, scale_max, *, k_ckpt, v_ckpt, ckpt_interval: int, out: torch.Tensor,
-                       mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False):
+                       mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False, half_state: bool = False):
     """The checkpointed decode step for a caller that must not allocate device memory.
 
     Same arguments and result as ``decode_attn(..., k_ckpt=, v_ckpt=, ckpt_interval=)``, except that ``out``
@@ -431,7 +461,7 @@ def decode_attn_static(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
             ctypes.addressof(kp), ctypes.addressof(vp), kc, vc, iv, cap, mptr, mstride, out.data_ptr(),
             B, Hq, Hkv, T, D, n_super_cap, bits, scaling, scale_min, scale_max,
-            _lib.FLAG_FAST_REPLAY if fast else 0, _stream(k_cache))
+            _lib.flags(fast, half_state), _stream(k_cache))
     _lib.check(rc, "decode_attn_static")
     return out
 

@@ -245,7 +245,7 @@ def run_reference(args, w, name):
 
 # --------------------------------------------------------------------------------------- GPU arm
 
-def build_gpu_state(w, seed, device, torch, ckpt_interval=0):
+def build_gpu_state(w, seed, device, torch, ckpt_interval=0, half_state=False):
     """Caches prefilled by the encode kernel from on-device synthetic K/V, plus the step's inputs."""
     from adkv_b200 import gemv, synth
     B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
@@ -268,7 +268,8 @@ def build_gpu_state(w, seed, device, torch, ckpt_interval=0):
             gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits,
                                 k_ckpt=kck[b0:b1], v_ckpt=vck[b0:b1], ckpt_interval=ckpt_interval)
         else:
-            gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+            gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits,
+                                half_state=half_state)
         del k, v
     q = synth.gen_q(seed + 2, B, Hq, D, device=device)
     kn = synth.gen_kv(seed + 5, B, Hkv, 1, D, device=device, pos0=T)
@@ -305,6 +306,23 @@ def check_against_oracle(w, st, out, n_streams, torch):
     ok = bool(np.allclose(got, want, rtol=2e-3, atol=tol)) and np.array_equal(kc, kc_after) and \
         np.array_equal(vc, vc_after)
     return ok, dt, n_streams, c_oracle.num_threads()
+
+
+def check_half(w, st, out):
+    """fp16-state arithmetic: the first sequence's output and appended codes against the numpy restatement."""
+    import numpy as np
+
+    from oracle import adkv_oracle_half as orh
+    D, T, bits = w["D"], w["T"], w["bits"]
+    kc_after, vc_after = st["kc"][:1].cpu().numpy(), st["vc"][:1].cpu().numpy()
+    kc, vc = kc_after.copy(), vc_after.copy()
+    f = lambda ps: tuple(p.cpu().numpy() for p in ps)
+    want, _ = orh.decode_attn(st["q"][:1, :, 0].cpu().numpy(), kc, vc, st["kn"][:1, :, 0].cpu().numpy(),
+                              st["vn"][:1, :, 0].cpu().numpy(), f(st["kp"]), f(st["vp"]), T, D ** -0.5, bits)
+    got = out[:1].float().cpu().numpy()
+    tol = 2e-2 * max(1.0, float(np.abs(want).max()))    # logits are summed in fp16, as in the reference's kernels
+    return bool(np.allclose(got, want, rtol=2e-2, atol=tol)) and np.array_equal(kc, kc_after) and \
+        np.array_equal(vc, vc_after)
 
 
 def time_cuda(fn, torch, device, steps, warmup=3):
@@ -356,8 +374,11 @@ def run_encode(args, w, name):
     tk = torch.empty((B, H, 2, D), dtype=torch.float32, device=device)
     tv = torch.empty_like(tk)
 
+    half = args.replay == "half"
+
     def step(ks=k, vs=v):
-        gemv.encode_kv_pair(kc, ks, kp, vc, vs, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, k_tail=tk, v_tail=tv)
+        gemv.encode_kv_pair(kc, ks, kp, vc, vs, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, k_tail=tk, v_tail=tv,
+                            half_state=half)
 
     prop = torch.cuda.get_device_properties(device)
     try:
@@ -388,7 +409,7 @@ def run_encode(args, w, name):
     a0.record()
     for i in range(w["appends"]):
         gemv.append_kv_pair(kc, kn[:, :, i:i + 1], kp, tk, vc, vn[:, :, i:i + 1], vp, tv, T + i,
-                            synth.SCALE_MIN, synth.SCALE_MAX, bits=bits)
+                            synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, half_state=half)
     a1.record()
     torch.cuda.synchronize(device)
     append_us = a0.elapsed_time(a1) * 1e3 / w["appends"]
@@ -422,7 +443,14 @@ def run_encode(args, w, name):
     cpu_dt = time.perf_counter() - tc0
     step()
     used = gemv.n_super_for(T, bits)
-    ok = np.array_equal(kc[:nb, :, :used].cpu().numpy(), kc_cpu[:, :, :used])
+    if half:   # fp16-state arithmetic: the first sequence against its numpy restatement
+        from oracle import adkv_oracle_half as orh
+        nb_chk = 1
+        kc_cpu = np.zeros((nb_chk, H, ns, D // 4, 4, 4), np.uint8)
+        orh.encode_kv(kc_cpu, xk[:nb_chk], tuple(p.cpu().numpy() for p in kp), bits)
+    else:
+        nb_chk = nb
+    ok = np.array_equal(kc[:nb_chk, :, :used].cpu().numpy(), kc_cpu[:, :, :used])
 
     nbytes = algorithmic_bytes(w)
     ref_cuda_leg = None
@@ -445,7 +473,7 @@ def run_encode(args, w, name):
         "metric": "adkv_prefill_quantize_bandwidth", "value": nbytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": UNIT,
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": dict(workload=name, per_gpu=w, l2="inputs larger than L2; no flush needed"),
+        "config": dict(workload=name, per_gpu=w, replay=args.replay, l2="inputs larger than L2; no flush needed"),
         "e2e": {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * k.numel() * 2,
                 "d2h_bytes_per_step": htail.numel() * 4, "ms_per_step": e2e_ms},
         "gpu_launches": args.steps,
@@ -484,7 +512,10 @@ def run_ours(args, w, name):
     if args.scaling == "strong" and world > 1:
         assert w["B"] % world == 0, "strong scaling splits the batch evenly"
         w["B"] //= world
-    st = build_gpu_state(w, seed=1000 + 7919 * rank, device=device, torch=torch, ckpt_interval=args.ckpt_interval)
+    half = args.replay == "half"
+    assert not (half and args.ckpt_interval), "state checkpoints belong to the fp32 recurrence"
+    st = build_gpu_state(w, seed=1000 + 7919 * rank, device=device, torch=torch, ckpt_interval=args.ckpt_interval,
+                         half_state=half)
     ck = st["ck"]
     B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
     scaling = D ** -0.5
@@ -493,7 +524,7 @@ def run_ours(args, w, name):
 
     def step():
         gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out, **ck)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, half_state=half, out=out, **ck)
 
     def barrier():
         if world > 1:
@@ -534,7 +565,7 @@ def run_ours(args, w, name):
         dk_.copy_(hk, non_blocking=True)
         dv_.copy_(hv, non_blocking=True)
         gemv.decode_attn(dq, st["kc"], st["vc"], dk_, dv_, st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, out=out, **ck)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, half_state=half, out=out, **ck)
         hout.copy_(out, non_blocking=True)
 
     for _ in range(max(3, min(args.warmup, 5))):
@@ -548,18 +579,17 @@ def run_ours(args, w, name):
     barrier()
     e2e_ms = e0.elapsed_time(e1)
 
-    # the other replay arithmetic, same workload, for the record (not the headline)
-    other = not fast
-    o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the other replay arithmetics, same workload and caches, for the record (not the headline)
+    others = []
     other_steps = max(1, min(args.steps, 50))
-    for it in range(3 + other_steps):
-        if it == 3:
-            o0.record()
-        gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=other, out=out, **ck)
-    o1.record()
-    barrier()
-    other_ms = o0.elapsed_time(o1) / other_steps
+    for mode in ("exact", "fast", "half"):
+        if mode == args.replay or (mode == "half" and args.ckpt_interval):
+            continue
+        ms = time_cuda(lambda: gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T,
+                                                scaling, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=mode == "fast",
+                                                half_state=mode == "half", out=out, **ck),
+                       torch, device, other_steps)
+        others.append([mode, ms])
     # the three-call sequence of the reference's caller (src/adkv/hf/llama_adkv.py:263-276): unscaled logits,
     # torch softmax in fp32, weighted sum -- through this library's kernels and, where it has been built and
     # covers the workload, through the reference's own CUDA kernels recompiled for sm_100a
@@ -573,7 +603,7 @@ def run_ours(args, w, name):
             return fn
         kc2, vc2 = st["kc"].clone(), st["vc"].clone()
         n_trio = max(1, min(args.steps, 20))
-        ms = time_cuda(trio(gemv.forward_qk, gemv.forward_ov, bits=bits, fast=fast), torch, device, n_trio)
+        ms = time_cuda(trio(gemv.forward_qk, gemv.forward_ov, bits=bits, fast=fast, half_state=half), torch, device, n_trio)
         trio_legs["unfused_trio"] = {"ms_per_step": ms, "value": algorithmic_bytes(w) / (ms * 1e-3) / 1e9, "unit": UNIT,
                                      "what": "forward_qk + torch softmax + forward_ov of this library"}
         ref = reference_cuda_module(w)
@@ -588,9 +618,10 @@ def run_ours(args, w, name):
     torch.cuda.synchronize(device)
 
     if world > 1:
-        t = torch.tensor([total_ms, e2e_ms, other_ms], dtype=torch.float64, device=device)
+        t = torch.tensor([total_ms, e2e_ms] + [ms for _, ms in others], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, other_ms = t.tolist()
+        total_ms, e2e_ms = t.tolist()[:2]
+        others = [[m, v] for (m, _), v in zip(others, t.tolist()[2:])]
 
     bytes_rank = algorithmic_bytes(w)
     res = None
@@ -620,11 +651,13 @@ def run_ours(args, w, name):
                          "algorithmic_bytes_per_launch": bytes_rank, "avg_launch_ms": avg_launch_ms,
                          "median_launch_ms": statistics.median(per_launch_ms)},
             "clocks": sampler.summary(t_wall0, t_wall1),
-            "other_replay": {"replay": "fast" if other else "exact", "ms_per_step": other_ms,
-                             "value": bytes_rank * world / (other_ms * 1e-3) / 1e9, "unit": UNIT},
+            "other_replay": [{"replay": m, "ms_per_step": ms, "value": bytes_rank * world / (ms * 1e-3) / 1e9,
+                              "unit": UNIT} for m, ms in others],
         }
         res.update(trio_legs)
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and half:
+            res["parity_check"] = "ok" if check_half(w, st, out) else "FAILED"
+        elif world == 1 and not args.no_cpu:
             n = pick_sample_streams(w, target_s=args.cpu_seconds)
             ok, dt, n_used, cores = check_against_oracle(w, st, out, n, torch)
             res["cpu_baseline"] = {"value": sample_bytes(w, n_used) / dt / 1e9, "unit": UNIT, "cores": cores,
@@ -648,7 +681,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
-    ap.add_argument("--replay", choices=["exact", "fast"], default="exact")
+    ap.add_argument("--replay", choices=["exact", "fast", "half"], default="exact",
+                    help="exact / fast: the fp32 recurrence (canonical order / contracted); half: the fp16-state "
+                         "arithmetic of the reference's CUDA kernels (ADKV_FLAG_HALF_STATE)")
     ap.add_argument("--ckpt-interval", type=int, default=0,
                     help="decode with state checkpoints every N tokens (segment-parallel kernel + merge)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)

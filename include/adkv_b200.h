@@ -24,7 +24,8 @@
  * order ("canonical").  ADKV_FLAG_FAST_REPLAY lets the decode kernels replay the cached
  * tokens with fused multiply-adds instead (zp = fma(alpha, q*s, zp), s = clamp(s * fma(beta, |q|, 1 - beta*target))): attention
  * outputs stay within tolerance, and an appended code may differ from the canonical one by
- * one step in rare cases.
+ * one step in rare cases.  ADKV_FLAG_HALF_STATE selects the OTHER arithmetic the reference has: the fp16 state of
+ * its CUDA kernels (src/adkv/kernel/gemv.cu:150-164), bit-compatible with caches those kernels wrote.
  */
 #ifndef ADKV_B200_H
 #define ADKV_B200_H
@@ -45,12 +46,22 @@ extern "C" {
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
 #define ADKV_E_SCRATCH   (-8)  /* the scratch memory given is smaller than the problem needs */
 #define ADKV_E_STATIC_MAX (-9) /* problem needs more than ADKV_STATIC_SCRATCH_BYTES of built-in scratch */
+#define ADKV_E_FLAGS     (-10) /* ADKV_FLAG_HALF_STATE is not available for this entry point / head dim */
 
 /* Size of the library's built-in scratch array (see adkv_decode_attn_ckpt_static). */
 #define ADKV_STATIC_SCRATCH_BYTES (16u << 20)
 
 /* flags */
 #define ADKV_FLAG_FAST_REPLAY 1u  /* decode kernels: contracted (FMA) replay of cached tokens */
+/* The arithmetic of the reference's own CUDA kernels instead of the fp32 definition: recurrence state and
+ * constants in fp16, zp <- fma(alpha, q*sc, zp), sc <- sc * fma(beta, |q|, 1 - beta*target), no eps guard, no
+ * scale clamp (scale_min / scale_max are ignored, as they are there), quantiser in fp32
+ * (src/adkv/kernel/gemv.cu:150-164).  Codes, appended codes and tail states are bit-identical to what the
+ * reference's encode_kv / forward_qk / forward_ov produce, so caches can be exchanged with them; logits and
+ * outputs are accumulated more accurately than there (fp32 across tokens) and agree within fp16 accumulation
+ * error.  Takes precedence over ADKV_FLAG_FAST_REPLAY.  Available for head dim 128 in the decode entry points
+ * (all head dims in the encode / append ones), not with state checkpoints: ADKV_E_FLAGS otherwise. */
+#define ADKV_FLAG_HALF_STATE 2u
 
 /* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each
  * (src/adkv/hf/llama_adkv.py:27: zp_init, scale_init, alpha, beta, quant_target). */
@@ -99,6 +110,19 @@ int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void
                    void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail,
                    int B, int H, int T, int D, int n_super_cap, int bits,
                    float scale_min, float scale_max, void *stream);
+
+/* adkv_encode_kv / adkv_append_kv with a `flags` argument (ADKV_FLAG_HALF_STATE selects the arithmetic of the
+ * reference's CUDA kernels; 0 is the same as the calls above).  v_cache == NULL: one tensor only (the K
+ * arguments).  The tail keeps its float [B, H, 2, D] format in both arithmetics (fp16 state values are stored
+ * exactly). */
+int adkv_encode_kv_flags(void *k_cache, const void *k, const adkv_params *kp, void *k_tail,
+                         void *v_cache, const void *v, const adkv_params *vp, void *v_tail,
+                         int B, int H, int T, int D, int n_super_cap, int bits, int t_start,
+                         float scale_min, float scale_max, unsigned flags, void *stream);
+int adkv_append_kv_flags(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail,
+                         void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail,
+                         int B, int H, int T, int D, int n_super_cap, int bits,
+                         float scale_min, float scale_max, unsigned flags, void *stream);
 
 /* q.K^T over the packed cache + append of k_new as token T + self logit.  Replaces forward_qk
  * (src/adkv/kernel/gemv.cu:883-939, called from src/adkv/hf/llama_adkv.py:264).
