@@ -69,10 +69,11 @@ class ADKVLlama:
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, bits: int = 4, device="cuda",
                  rank: int = 0, world: int = 1, seed: int = 0, fused: bool = True, fast: bool = False,
-                 ckpt_interval: int = 0):
+                 ckpt_interval: int = 0, half_state: bool = False):
         assert shape.n_heads % world == 0 and shape.n_kv_heads % world == 0 and shape.ffn % world == 0
         self.s, self.B, self.bits, self.dev = shape, batch, bits, torch.device(device)
         self.rank, self.world, self.fused, self.fast, self.ckpt_interval = rank, world, fused, fast, ckpt_interval
+        self.half_state = half_state
         self.hq, self.hkv, self.ffn = shape.n_heads // world, shape.n_kv_heads // world, shape.ffn // world
         D, dm = shape.head_dim, shape.d_model
         g = torch.Generator(device=self.dev)
@@ -161,7 +162,7 @@ class ADKVLlama:
                 q, k, v = self._qkv(L, h, Tp)
                 q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
                 gemv.encode_kv_pair(L["kc"][b0:b1], k.contiguous(), L["kp"], L["vc"][b0:b1], v.contiguous(), L["vp"],
-                                    synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits,
+                                    synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, half_state=self.half_state,
                                     **({"k_ckpt": L["kck"][b0:b1], "v_ckpt": L["vck"][b0:b1],
                                         "ckpt_interval": self.ckpt_interval} if self.ckpt_interval else {}))
                 att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.hq != self.hkv)
@@ -187,7 +188,7 @@ class ADKVLlama:
             q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
             att = gemv.decode_attn_varlen(q, L["kc"], L["vc"], k, v.contiguous(), L["kp"], L["vp"], self.seq_lens,
                                           self.scaling, synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits,
-                                          fast=self.fast)
+                                          fast=self.fast, half_state=self.half_state)
             x = x + self._allreduce(att.reshape(self.B, 1, -1) @ L["wo"].T)
             x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
         self.seq_lens += 1
@@ -235,14 +236,14 @@ class ADKVLlama:
             v = v.contiguous()
             if self.fused:
                 att = gemv.decode_attn(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], T, self.scaling,
-                                       synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, fast=self.fast,
+                                       synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, fast=self.fast, half_state=self.half_state,
                                        scratch=self.scratch, **self._ck(L))
             else:   # the reference caller's three-call sequence (llama_adkv.py:263-276)
                 logits = gemv.forward_qk(q, L["kc"], k, *L["kp"], T, synth.SCALE_MIN, synth.SCALE_MAX,
-                                         bits=self.bits, fast=self.fast)
+                                         bits=self.bits, fast=self.fast, half_state=self.half_state)
                 w = torch.softmax(logits.float() * self.scaling, dim=-1).to(torch.float16)
                 att = gemv.forward_ov(w, L["vc"], v, *L["vp"], synth.SCALE_MIN, synth.SCALE_MAX,
-                                      bits=self.bits, fast=self.fast)
+                                      bits=self.bits, fast=self.fast, half_state=self.half_state)
             x = x + self._allreduce(att.reshape(self.B, 1, -1) @ L["wo"].T)
             x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
         self.T = T + 1
@@ -251,7 +252,7 @@ class ADKVLlama:
 
 
 def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fused: bool = True, fast: bool = False,
-        ckpt_interval: int = 0, seed: int = 0, graph: bool = False) -> dict:
+        ckpt_interval: int = 0, seed: int = 0, graph: bool = False, half_state: bool = False) -> dict:
     """Prefill a random prompt, generate `gen` tokens greedily; timings with CUDA events, max over ranks."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -261,7 +262,7 @@ def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fus
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     model = ADKVLlama(shape, batch, prompt + gen, bits=bits, device=dev, rank=rank, world=world, seed=seed,
-                      fused=fused, fast=fast, ckpt_interval=ckpt_interval)
+                      fused=fused, fast=fast, ckpt_interval=ckpt_interval, half_state=half_state)
     g = torch.Generator(device=dev)
     g.manual_seed(seed + 99)
     ids = torch.randint(0, shape.vocab, (batch, prompt), generator=g, device=dev)
@@ -308,17 +309,19 @@ def main():
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--unfused", action="store_true")
     ap.add_argument("--fast", action="store_true")
+    ap.add_argument("--half-state", action="store_true",
+                    help="the fp16-state arithmetic of the reference's CUDA kernels instead of the fp32 recurrence")
     ap.add_argument("--ckpt-interval", type=int, default=0)
     ap.add_argument("--graph", action="store_true", help="replay the decode step from a CUDA graph (device-side lengths)")
     a = ap.parse_args()
     shape = LlamaShape(n_layers=a.layers)
     r = run(shape, a.batch, a.prompt, a.gen, bits=a.bits, fused=not a.unfused, fast=a.fast,
-            ckpt_interval=a.ckpt_interval, graph=a.graph)
+            ckpt_interval=a.ckpt_interval, graph=a.graph, half_state=a.half_state)
     if r["rank"] == 0:
         r.pop("tokens")
         r.update(metric="e2e_decode_tokens_per_s", config=dict(model="random-init Llama-2-7B architecture", batch=a.batch,
                  prompt=a.prompt, generate=a.gen, layers=a.layers, bits=a.bits, fused=not a.unfused,
-                 replay="fast" if a.fast else "exact", tensor_parallel=r["world"], cuda_graph=a.graph,
+                 replay="half" if a.half_state else ("fast" if a.fast else "exact"), tensor_parallel=r["world"], cuda_graph=a.graph,
                  data="synthetic"))
         print(json.dumps(r), flush=True)
     if dist.is_initialized():
