@@ -64,7 +64,7 @@ using namespace adkv;
 ADKV_HIDDEN int adkv_half_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
                                       float scaling, int B, int bits, const int *seq_lens, cudaStream_t s);
 ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
-                                      float scaling, int B, int bits, bool exact, cudaStream_t s);
+                                      float scaling, int B, int bits, int mode, cudaStream_t s);
 
 // Status word of this translation unit (read and cleared by adkv_device_status).
 ADKV_HIDDEN int adkv_tu_status_fused(int *out)
@@ -95,11 +95,12 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
                    to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ADKV_FLAG_HALF_STATE)
-        return adkv_half_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, nullptr, s);
-    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    const bool half = flags & ADKV_FLAG_HALF_STATE, exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     if (D != kD)
-        return adkv_wide_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, exact, s);
+        return adkv_wide_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits,
+                                     half ? 2 : int(exact), s);
+    if (half)
+        return adkv_half_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, nullptr, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(
                       ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, nullptr)))

@@ -63,8 +63,8 @@ using namespace adkv;
 
 ADKV_HIDDEN int adkv_half_forward_qk(const KArgs &ka, __half *logits, int B, int bits, cudaStream_t s);
 ADKV_HIDDEN int adkv_half_forward_ov(const VArgs &va, const __half *attn, int B, int bits, cudaStream_t s);
-ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, bool exact, cudaStream_t s);
-ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, bool exact, cudaStream_t s);
+ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, int mode, cudaStream_t s);
+ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, int mode, cudaStream_t s);
 
 // Status word of this translation unit (read and cleared by adkv_device_status).
 ADKV_HIDDEN int adkv_tu_status_unfused(int *out)
@@ -90,9 +90,9 @@ int adkv_forward_qk(const void *q, void *k_cache, const void *k_new, const adkv_
                    static_cast<const __half *>(k_new), to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ADKV_FLAG_HALF_STATE) return adkv_half_forward_qk(ka, static_cast<__half *>(logits), B, bits, s);
-    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
-    if (D != kD) return adkv_wide_forward_qk(ka, static_cast<__half *>(logits), B, bits, exact, s);
+    const bool half = flags & ADKV_FLAG_HALF_STATE, exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    if (D != kD) return adkv_wide_forward_qk(ka, static_cast<__half *>(logits), B, bits, half ? 2 : int(exact), s);
+    if (half) return adkv_half_forward_qk(ka, static_cast<__half *>(logits), B, bits, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (forward_qk_kernel<BITS, G, EXACT><<<grid, 32 * kStreamsPerCta, 0, s>>>(
                       ka, static_cast<__half *>(logits), n_streams)))
@@ -111,9 +111,9 @@ int adkv_forward_ov(const void *attn, void *v_cache, const void *v_new, const ad
                    to_ptrs(p), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const int n_streams = B * Hkv, grid = (n_streams + kStreamsPerCta - 1) / kStreamsPerCta;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ADKV_FLAG_HALF_STATE) return adkv_half_forward_ov(va, static_cast<const __half *>(attn), B, bits, s);
-    const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
-    if (D != kD) return adkv_wide_forward_ov(va, static_cast<const __half *>(attn), B, bits, exact, s);
+    const bool half = flags & ADKV_FLAG_HALF_STATE, exact = !(flags & ADKV_FLAG_FAST_REPLAY);
+    if (D != kD) return adkv_wide_forward_ov(va, static_cast<const __half *>(attn), B, bits, half ? 2 : int(exact), s);
+    if (half) return adkv_half_forward_ov(va, static_cast<const __half *>(attn), B, bits, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (forward_ov_kernel<BITS, G, EXACT><<<grid, 32 * kStreamsPerCta, 0, s>>>(
                       va, static_cast<const __half *>(attn), n_streams)))

@@ -7,9 +7,30 @@
 // ring slot and every consumer adds the S partials (no atomics, fixed summation order).
 #include "adkv_host.h"
 
+#include "adkv_half.cuh"
 #include "adkv_softmax.cuh"
 
 namespace adkv {
+
+// MODE: 0 = fp32 recurrence, contracted replay; 1 = fp32 recurrence, canonical order; 2 = the fp16-state
+// arithmetic of the reference's kernels (adkv_half.cuh).
+constexpr int kModeHalf = 2;
+
+template <int BITS, int G, int MODE, class Sink, int ST>
+__device__ __forceinline__ void k_scan(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
+                                       float *red, Sink &sink)
+{
+    if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST>(a, seg, b, h, lane, buf, bar, red, sink);
+    else k_warp<BITS, G, MODE == 1, Sink, ST>(a, seg, b, h, lane, buf, bar, red, sink);
+}
+
+template <int BITS, int G, int MODE, class Src, int ST>
+__device__ __forceinline__ void v_scan(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
+                                       const float2 *wts, Src &src)
+{
+    if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST>(a, seg, b, h, lane, buf, bar, wts, src);
+    else v_warp<BITS, G, MODE == 1, Src, ST>(a, seg, b, h, lane, buf, bar, wts, src);
+}
 
 template <int S>
 struct WideCfg {
@@ -17,7 +38,7 @@ struct WideCfg {
 };
 
 // ------------------------------------------------------------------------------------------ fused
-template <int BITS, int G, bool EXACT, int S>
+template <int BITS, int G, int MODE, int S>
 __global__ void __launch_bounds__(64 * S) decode_attn_wide_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
                                                                   long long mask_stride_b, float scaling)
 {
@@ -42,9 +63,9 @@ __global__ void __launch_bounds__(64 * S) decode_attn_wide_kernel(KArgs ka, VArg
     const Seg seg{0, ka.T, true, nullptr, nullptr, sl};
     if (role == 0) {
         RingSink<G, S> sink{&fs, 0, sl};
-        k_warp<BITS, G, EXACT, RingSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
+        k_scan<BITS, G, MODE, RingSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
     } else {
-        SoftmaxSrc<G, S> src;
+        SoftmaxSrc<G, S, MODE == kModeHalf> src;
         src.sh = &fs;
         src.wts = wts[sl];
         src.mask = mask ? mask + size_t(b) * mask_stride_b : nullptr;
@@ -52,7 +73,7 @@ __global__ void __launch_bounds__(64 * S) decode_attn_wide_kernel(KArgs ka, VArg
         src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
         src.t_begin = 0;
         src.init();
-        v_warp<BITS, G, EXACT, SoftmaxSrc<G, S>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
+        v_scan<BITS, G, MODE, SoftmaxSrc<G, S, MODE == kModeHalf>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
     }
 }
 
@@ -92,7 +113,7 @@ struct WriterSink : RingSink<G, S> {
     }
 };
 
-template <int BITS, int G, bool EXACT, int S>
+template <int BITS, int G, int MODE, int S>
 __global__ void __launch_bounds__(32 * S) forward_qk_wide_kernel(KArgs ka, __half *__restrict__ logits)
 {
     constexpr int ST = WideCfg<S>::STAGES;
@@ -118,15 +139,15 @@ __global__ void __launch_bounds__(32 * S) forward_qk_wide_kernel(KArgs ka, __hal
         sink.T = ka.T;
 #pragma unroll
         for (int g = 0; g < G; ++g) sink.row[g] = logits + (size_t(b) * ka.Hq + size_t(h) * G + g) * (ka.T + 1);
-        k_warp<BITS, G, EXACT, WriterSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[0], kbar[0], red[0], sink);
+        k_scan<BITS, G, MODE, WriterSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[0], kbar[0], red[0], sink);
     } else {
         RingSink<G, S> sink{&fs, 0, sl};
-        k_warp<BITS, G, EXACT, RingSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
+        k_scan<BITS, G, MODE, RingSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
     }
 }
 
 // ------------------------------------------------------------------------------------------ P.V
-template <int G>
+template <int G, bool HALF_W>
 struct WideWeightSrc {
     const __half *row[G];
     float2 *wts;
@@ -135,7 +156,7 @@ struct WideWeightSrc {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             const float wv = lane < ntok ? __half2float(row[g][i * kTileTok + lane]) : 0.f;
-            wts[g * kTileTok + lane] = make_float2(wv, wv);
+            put_weight<HALF_W>(wts, g * kTileTok + lane, wv);
         }
         __syncwarp();
         return true;
@@ -153,7 +174,7 @@ struct WideWeightSrc {
     }
 };
 
-template <int BITS, int G, bool EXACT, int S>
+template <int BITS, int G, int MODE, int S>
 __global__ void __launch_bounds__(32 * S) forward_ov_wide_kernel(VArgs va, const __half *__restrict__ attn)
 {
     constexpr int ST = WideCfg<S>::STAGES;
@@ -167,29 +188,29 @@ __global__ void __launch_bounds__(32 * S) forward_ov_wide_kernel(VArgs va, const
         mbar_init_fence();
     }
     __syncthreads();
-    WideWeightSrc<G> src;
+    WideWeightSrc<G, MODE == kModeHalf> src;
 #pragma unroll
     for (int g = 0; g < G; ++g) src.row[g] = attn + (size_t(b) * va.Hq + size_t(h) * G + g) * (va.T + 1);
     src.wts = wts[sl];
     const Seg seg{0, va.T, true, nullptr, nullptr, sl};
-    v_warp<BITS, G, EXACT, WideWeightSrc<G>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
+    v_scan<BITS, G, MODE, WideWeightSrc<G, MODE == kModeHalf>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
 }
 
 // Dispatch over (bits, arithmetic, slices, group size); group sizes are limited by the 48 KB of static shared memory.
-#define ADKV_WIDE_G(BITS_, EXACT_, S_, G_, CALL)                                                              \
-    { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int S = S_; constexpr int G = G_; CALL; }
-#define ADKV_WIDE_S(BITS_, EXACT_, S_, g_, CALL)                                  \
-    if (g_ == 1) ADKV_WIDE_G(BITS_, EXACT_, S_, 1, CALL)                          \
-    else if (g_ == 2) ADKV_WIDE_G(BITS_, EXACT_, S_, 2, CALL)                     \
+#define ADKV_WIDE_G(BITS_, MODE_, S_, G_, CALL)                                                               \
+    { constexpr int BITS = BITS_; constexpr int MODE = MODE_; constexpr int S = S_; constexpr int G = G_; CALL; }
+#define ADKV_WIDE_S(BITS_, MODE_, S_, g_, CALL)                                   \
+    if (g_ == 1) ADKV_WIDE_G(BITS_, MODE_, S_, 1, CALL)                           \
+    else if (g_ == 2) ADKV_WIDE_G(BITS_, MODE_, S_, 2, CALL)                      \
     else return ADKV_E_SHAPE;
-#define ADKV_WIDE_E(BITS_, EXACT_, s_, g_, CALL)                                  \
-    if (s_ == 2) { ADKV_WIDE_S(BITS_, EXACT_, 2, g_, CALL) } else { ADKV_WIDE_S(BITS_, EXACT_, 4, g_, CALL) }
-#define ADKV_WIDE_DISPATCH(bits_, exact_, s_, g_, CALL)                                                    \
-    if (bits_ == 4) {                                                                                      \
-        if (exact_) { ADKV_WIDE_E(4, true, s_, g_, CALL) } else { ADKV_WIDE_E(4, false, s_, g_, CALL) }     \
-    } else {                                                                                               \
-        if (exact_) { ADKV_WIDE_E(2, true, s_, g_, CALL) } else { ADKV_WIDE_E(2, false, s_, g_, CALL) }     \
-    }
+#define ADKV_WIDE_E(BITS_, MODE_, s_, g_, CALL)                                   \
+    if (s_ == 2) { ADKV_WIDE_S(BITS_, MODE_, 2, g_, CALL) } else { ADKV_WIDE_S(BITS_, MODE_, 4, g_, CALL) }
+#define ADKV_WIDE_M(BITS_, mode_, s_, g_, CALL)                                   \
+    if (mode_ == 2) { ADKV_WIDE_E(BITS_, 2, s_, g_, CALL) }                       \
+    else if (mode_ == 1) { ADKV_WIDE_E(BITS_, 1, s_, g_, CALL) }                  \
+    else { ADKV_WIDE_E(BITS_, 0, s_, g_, CALL) }
+#define ADKV_WIDE_DISPATCH(bits_, mode_, s_, g_, CALL)                            \
+    if (bits_ == 4) { ADKV_WIDE_M(4, mode_, s_, g_, CALL) } else { ADKV_WIDE_M(2, mode_, s_, g_, CALL) }
 
 }  // namespace adkv
 
@@ -207,28 +228,28 @@ ADKV_HIDDEN int adkv_tu_status_wide(int *out)
 
 // Called by the public entry points for D = 256 / 512 after argument validation.
 ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
-                                      float scaling, int B, int bits, bool exact, cudaStream_t s)
+                                      float scaling, int B, int bits, int mode, cudaStream_t s)
 {
     const int S = ka.D / kD, g = ka.Hq / ka.Hkv;
-    ADKV_WIDE_DISPATCH(bits, exact, S, g,
-                       (decode_attn_wide_kernel<BITS, G, EXACT, S><<<B * ka.Hkv, 64 * S, 0, s>>>(ka, va, mask,
+    ADKV_WIDE_DISPATCH(bits, mode, S, g,
+                       (decode_attn_wide_kernel<BITS, G, MODE, S><<<B * ka.Hkv, 64 * S, 0, s>>>(ka, va, mask,
                                                                                                   mask_stride_b,
                                                                                                   scaling)))
     return launch_status();
 }
 
-ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, bool exact, cudaStream_t s)
+ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, int mode, cudaStream_t s)
 {
     const int S = ka.D / kD, g = ka.Hq / ka.Hkv;
-    ADKV_WIDE_DISPATCH(bits, exact, S, g,
-                       (forward_qk_wide_kernel<BITS, G, EXACT, S><<<B * ka.Hkv, 32 * S, 0, s>>>(ka, logits)))
+    ADKV_WIDE_DISPATCH(bits, mode, S, g,
+                       (forward_qk_wide_kernel<BITS, G, MODE, S><<<B * ka.Hkv, 32 * S, 0, s>>>(ka, logits)))
     return launch_status();
 }
 
-ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, bool exact, cudaStream_t s)
+ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, int mode, cudaStream_t s)
 {
     const int S = va.D / kD, g = va.Hq / va.Hkv;
-    ADKV_WIDE_DISPATCH(bits, exact, S, g,
-                       (forward_ov_wide_kernel<BITS, G, EXACT, S><<<B * va.Hkv, 32 * S, 0, s>>>(va, attn)))
+    ADKV_WIDE_DISPATCH(bits, mode, S, g,
+                       (forward_ov_wide_kernel<BITS, G, MODE, S><<<B * va.Hkv, 32 * S, 0, s>>>(va, attn)))
     return launch_status();
 }

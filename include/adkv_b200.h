@@ -46,7 +46,7 @@ extern "C" {
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
 #define ADKV_E_SCRATCH   (-8)  /* the scratch memory given is smaller than the problem needs */
 #define ADKV_E_STATIC_MAX (-9) /* problem needs more than ADKV_STATIC_SCRATCH_BYTES of built-in scratch */
-#define ADKV_E_FLAGS     (-10) /* ADKV_FLAG_HALF_STATE is not available for this entry point / head dim */
+#define ADKV_E_FLAGS     (-10) /* ADKV_FLAG_HALF_STATE is not available for this entry point */
 
 /* Size of the library's built-in scratch array (see adkv_decode_attn_ckpt_static). */
 #define ADKV_STATIC_SCRATCH_BYTES (16u << 20)
@@ -59,8 +59,8 @@ extern "C" {
  * (src/adkv/kernel/gemv.cu:150-164).  Codes, appended codes and tail states are bit-identical to what the
  * reference's encode_kv / forward_qk / forward_ov produce, so caches can be exchanged with them; logits and
  * outputs are accumulated more accurately than there (fp32 across tokens) and agree within fp16 accumulation
- * error.  Takes precedence over ADKV_FLAG_FAST_REPLAY.  Available for head dim 128 in the decode entry points
- * (all head dims in the encode / append ones), not with state checkpoints: ADKV_E_FLAGS otherwise. */
+ * error.  Takes precedence over ADKV_FLAG_FAST_REPLAY.  Available wherever the head dim is (128 / 256 / 512 in
+ * encode, append, forward_qk, forward_ov and decode_attn), except with state checkpoints: ADKV_E_FLAGS. */
 #define ADKV_FLAG_HALF_STATE 2u
 
 /* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each

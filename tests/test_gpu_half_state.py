@@ -259,3 +259,52 @@ def test_generation_with_cache_object_leaves_the_reference_kernels_caches():
         a, b = o.float().reshape(B, H, D), ro.float()
         torch.testing.assert_close(b, a, rtol=3e-2, atol=3e-2 * max(1.0, float(a.abs().max())))
     assert torch.equal(rk, layer.key_states) and torch.equal(rv, layer.value_states)
+
+
+# ------------------------------------------------------------------------------------ head dims 256 / 512
+
+def _wide_params(seed, H, Dw):
+    g = torch.Generator().manual_seed(seed)
+    p = (torch.randn(H, Dw, generator=g) * 0.5, torch.rand(H, Dw, generator=g) * 1.5 + 0.3,
+         torch.rand(H, Dw, generator=g) * 0.2, torch.rand(H, Dw, generator=g) * 0.08,
+         torch.rand(H, Dw, generator=g) * 4 + 0.5)
+    return tuple(t.half().cuda() for t in p)
+
+
+@needs_ref
+@pytest.mark.parametrize("Dw", [256, 512])
+@pytest.mark.parametrize("T", [0, 9, 77, 300])
+def test_wide_heads_equal_reference_kernels(Dw, T):
+    B, H = 2, 3
+    ref = ref_cuda.module()
+    k = synth.gen_kv(1500 + T, B, H, T + 1, Dw, outlier_mode="persistent").cuda()
+    v = synth.gen_kv(1501 + T, B, H, T + 1, Dw, outlier_mode="persistent").cuda()
+    q = synth.gen_q(1502 + T, B, H, Dw).cuda()
+    kp, vp = _wide_params(T, H, Dw), _wide_params(T + 1, H, Dw)
+    shape = orc.cache_shape(B, H, orc.n_super_for(T + 1, 4) + 1, Dw)
+    kc, vc = (torch.zeros(shape, dtype=torch.uint8, device="cuda") for _ in range(2))
+    rk, rv = torch.zeros_like(kc), torch.zeros_like(vc)
+    if T:
+        gemv.encode_kv_pair(kc, k[:, :, :T].contiguous(), kp, vc, v[:, :, :T].contiguous(), vp, SMIN, SMAX, half_state=True)
+        ref.encode_kv(rk, k[:, :, :T].contiguous(), *kp, SMIN, SMAX)
+        ref.encode_kv(rv, v[:, :, :T].contiguous(), *vp, SMIN, SMAX)
+        assert torch.equal(kc, rk) and torch.equal(vc, rv)
+    kn, vn = k[:, :, T:].contiguous(), v[:, :, T:].contiguous()
+    fk, fv = kc.clone(), vc.clone()
+    lt = ref.forward_qk(q, rk, kn, *kp, T, SMIN, SMAX)
+    lm = gemv.forward_qk(q, kc, kn, *kp, T, SMIN, SMAX, half_state=True)
+    assert torch.equal(kc, rk)
+    a, b = lm.float().cpu().numpy(), lt.float().cpu().numpy()
+    np.testing.assert_allclose(b, a, rtol=3e-2, atol=3e-2 * max(1.0, np.abs(a).max()))
+    attn = torch.softmax(lm.float() * Dw ** -0.5, dim=-1).half()
+    ot = ref.forward_ov(attn, rv, vn, *vp, SMIN, SMAX)
+    om = gemv.forward_ov(attn, vc, vn, *vp, SMIN, SMAX, half_state=True)
+    assert torch.equal(vc, rv)
+    a, b = om.float().cpu().numpy().reshape(B * H, Dw), ot.float().cpu().numpy().reshape(B * H, Dw)
+    np.testing.assert_allclose(b, a, rtol=3e-2, atol=3e-2 * max(1.0, np.abs(a).max()))
+    # fused step: same appended codes, output close to the three calls
+    of = gemv.decode_attn(q, fk, fv, kn, vn, kp, vp, T, Dw ** -0.5, SMIN, SMAX, half_state=True)
+    assert torch.equal(fk, kc) and torch.equal(fv, vc)
+    f = of.float().cpu().numpy().reshape(B * H, Dw)
+    np.testing.assert_allclose(f, a, rtol=3e-2, atol=3e-2 * max(1.0, np.abs(a).max()))
+    assert gemv.device_status() == 0
