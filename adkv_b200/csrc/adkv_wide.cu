@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(64 * S) decode_attn_wide_kernel(KArgs ka, VArg
         src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
         src.t_begin = 0;
         src.init();
-        v_scan<BITS, G, MODE, SoftmaxSrc<G, S, MODE == kModeHalf>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
+        v_scan<BITS, G, MODE, SoftmaxSrc<G, S, MODE == kModeHalf>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl],
+                                                                       src);
     }
 }
 

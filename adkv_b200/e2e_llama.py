@@ -236,8 +236,8 @@ class ADKVLlama:
             v = v.contiguous()
             if self.fused:
                 att = gemv.decode_attn(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], T, self.scaling,
-                                       synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, fast=self.fast, half_state=self.half_state,
-                                       scratch=self.scratch, **self._ck(L))
+                                       synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, fast=self.fast,
+                                       half_state=self.half_state, scratch=self.scratch, **self._ck(L))
             else:   # the reference caller's three-call sequence (llama_adkv.py:263-276)
                 logits = gemv.forward_qk(q, L["kc"], k, *L["kp"], T, synth.SCALE_MIN, synth.SCALE_MAX,
                                          bits=self.bits, fast=self.fast, half_state=self.half_state)
@@ -321,8 +321,8 @@ def main():
         r.pop("tokens")
         r.update(metric="e2e_decode_tokens_per_s", config=dict(model="random-init Llama-2-7B architecture", batch=a.batch,
                  prompt=a.prompt, generate=a.gen, layers=a.layers, bits=a.bits, fused=not a.unfused,
-                 replay="half" if a.half_state else ("fast" if a.fast else "exact"), tensor_parallel=r["world"], cuda_graph=a.graph,
-                 data="synthetic"))
+                 replay="half" if a.half_state else ("fast" if a.fast else "exact"), tensor_parallel=r["world"],
+                 cuda_graph=a.graph, data="synthetic"))
         print(json.dumps(r), flush=True)
     if dist.is_initialized():
         dist.barrier()

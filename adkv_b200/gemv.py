@@ -5,7 +5,8 @@ arguments, in-place semantics and error behaviour (``src/adkv/kernel/gemv.py:16-
 checks of ``src/adkv/kernel/gemv.cu:375-398, 892-912, 1241-1266``), so the reference's model file
 ``src/adkv/hf/llama_adkv.py`` runs on top of this module unchanged (see ``adkv_b200.hf_shim``).
 They call hand-written sm_100a kernels through the C ABI of ``libadkv_b200.so`` on the current
-torch CUDA stream.  Keyword-only extensions: ``bits`` (4 or 2), ``fast`` (contracted replay),
+torch CUDA stream.  Keyword-only extensions: ``bits`` (4 or 2), ``fast`` (contracted replay), ``half_state`` (the
+fp16-state arithmetic of the reference's CUDA kernels instead of the fp32 recurrence: bit-compatible caches),
 grouped-query heads (``q`` may have a multiple of the cache's heads).
 
 ``decode_attn`` is the fused decode step (q.K^T, scaling, mask, softmax, P.V and both appends in one
@@ -311,8 +312,8 @@ def decode_scratch_bytes(B: int, Hq: int, Hkv: int, T: int, interval: int) -> in
 
 def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
                 scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False,
-                half_state: bool = False, out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None, ckpt_interval: int = 0,
-                scratch: torch.Tensor | None = None):
+                half_state: bool = False, out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None,
+                ckpt_interval: int = 0, scratch: torch.Tensor | None = None):
     """Fused decode step over both packed caches.
 
     ``q [B, nh_q, 1, DIM]``, ``k_new`` / ``v_new [B, nh_kv, 1, DIM]`` float16; ``k_params`` / ``v_params``
