@@ -36,8 +36,31 @@ def n_super_for(tokens: int, bits: int = 4) -> int:
     return (tokens + tpw - 1) // tpw
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    """The caller's current CUDA stream on the tensor's device, as the C ABI takes it."""
+    if _raw_stream is not None:     # the handle itself, without building a torch.cuda.Stream object per call
+        return ctypes.c_void_p(_raw_stream(t.device.index))
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` that costs nothing when ``dev`` is already current (the usual case)."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev: torch.device):
+        self.ctx = None if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
 
 
 def _require(cond: bool, msg: str) -> None:
@@ -45,13 +68,29 @@ def _require(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
+# Parameter tensors are the same five objects call after call (one set per layer and tensor): the checked
+# ``adkv_params`` struct is remembered per set.  An entry holds the tensors, so their ids cannot be reused while it
+# is cached; a tensor whose storage was swapped since is caught by comparing the pointers.
+_PARAM_CACHE: dict = {}
+_PARAM_CACHE_MAX = 1024
+
+
 def _params(names, tensors, H, D, device):
+    key = tuple(map(id, tensors))
+    hit = _PARAM_CACHE.get(key)
+    if hit is not None and hit[2] == (H, D, device) and hit[3] == tuple(t.data_ptr() for t in tensors):
+        return hit[0], hit[1]
     for n, t in zip(names, tensors):
         _require(t.dtype == torch.float16, f"{n} must be float16")
         _require(t.is_cuda and t.device == device, f"{n} must be on the cache's CUDA device")
         _require(t.numel() == H * D, f"{n} must have {H} x {D} elements")
     keep = [t.contiguous() for t in tensors]
-    return _lib.Params(*[t.data_ptr() for t in keep]), keep
+    p = _lib.Params(*[t.data_ptr() for t in keep])
+    if len(_PARAM_CACHE) >= _PARAM_CACHE_MAX:
+        _PARAM_CACHE.clear()
+    # `tensors` are kept too: an id stays taken for as long as its object lives
+    _PARAM_CACHE[key] = (p, keep, (H, D, device), tuple(t.data_ptr() for t in tensors), tuple(tensors))
+    return p, keep
 
 
 def _cache_dims(cache: torch.Tensor, name: str):
@@ -87,7 +126,7 @@ def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min
     if tail is not None:
         _require(tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape == (B, H, 2, D),
                  "tail must be contiguous float32 [B, nh, 2, DIM]")
-    with torch.cuda.device(kv_cache.device):
+    with _on_device(kv_cache.device):
         if half_state:
             rc = _lib.load().adkv_encode_kv_flags(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
                                                   None if tail is None else tail.data_ptr(), None, None, None, None,
@@ -153,7 +192,7 @@ def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
     _require(not (half_state and ckpt_interval), "state checkpoints belong to the fp32 recurrence (no half_state)")
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         if half_state:
             rc = _lib.load().adkv_encode_kv_flags(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
                                                   _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
@@ -193,7 +232,7 @@ def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
     _require(not (half_state and ckpt_interval), "state checkpoints belong to the fp32 recurrence (no half_state)")
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         if half_state:
             rc = _lib.load().adkv_append_kv_flags(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
                                                   _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
@@ -230,7 +269,7 @@ def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min
              "tail must be contiguous float32 [B, nh, 2, DIM]")
     p, keep = _params(("zp", "sc", "alpha", "beta", "target"), (zp, sc, alpha, beta, target), H, D, cache.device)
     x = x_new.contiguous()
-    with torch.cuda.device(cache.device):
+    with _on_device(cache.device):
         if half_state:
             rc = _lib.load().adkv_append_kv_flags(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
                                                   None, None, None, None, B, H, T, D, n_super_cap, bits, scale_min,
@@ -265,7 +304,7 @@ def forward_qk(q, k_cache, k_new, k_zp, k_sc, k_alpha, k_beta, k_t, T: int, scal
                       Hkv, D, k_cache.device)
     qc, kn = q.contiguous(), k_new.contiguous()
     o = torch.empty((B, Hq, T + 1), dtype=torch.float16, device=k_cache.device)
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         rc = _lib.load().adkv_forward_qk(qc.data_ptr(), k_cache.data_ptr(), kn.data_ptr(), ctypes.addressof(p),
                                          o.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scale_min, scale_max,
                                          _lib.flags(fast, half_state), _stream(k_cache))
@@ -295,7 +334,7 @@ def forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min
                       Hkv, D, v_cache.device)
     ac, vn = attn.contiguous(), v_new.contiguous()
     o = torch.empty((B, Hq, D), dtype=torch.float16, device=v_cache.device)
-    with torch.cuda.device(v_cache.device):
+    with _on_device(v_cache.device):
         rc = _lib.load().adkv_forward_ov(ac.data_ptr(), v_cache.data_ptr(), vn.data_ptr(), ctypes.addressof(p),
                                          o.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scale_min, scale_max,
                                          _lib.flags(fast, half_state), _stream(v_cache))
@@ -353,7 +392,7 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
     flags = _lib.flags(fast, half_state)
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         if ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, Hkv, D)
             need = decode_scratch_bytes(B, Hq, Hkv, T, iv)
@@ -406,7 +445,7 @@ def decode_attn_varlen(q, k_cache, v_cache, k_new, v_new, k_params, v_params, se
     else:
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         rc = _lib.load().adkv_decode_attn_varlen(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
                                                  vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp),
                                                  seq_lens.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, n_super_cap,
@@ -457,7 +496,7 @@ def decode_attn_static(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T:
         _require(mask.dtype == torch.float32 and mask.is_cuda and mask.is_contiguous() and
                  tuple(mask.shape) == (B, T + 1), "mask must be a contiguous float32 [B, T + 1] CUDA tensor")
         mptr, mstride = mask.data_ptr(), T + 1
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         rc = _lib.load().adkv_decode_attn_ckpt_static(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
             ctypes.addressof(kp), ctypes.addressof(vp), kc, vc, iv, cap, mptr, mstride, out.data_ptr(),
@@ -471,7 +510,8 @@ def device_status(device=None) -> int:
     """Read and clear the device status word (non-zero: a kernel gave up on a bounded wait)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     val = ctypes.c_int(0)
-    with torch.cuda.device(dev):
-        rc = _lib.load().adkv_device_status(ctypes.byref(val), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    with _on_device(dev):
+        rc = _lib.load().adkv_device_status(ctypes.byref(val),
+                                            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _lib.check(rc, "device_status")
     return val.value
