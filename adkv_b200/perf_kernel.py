@@ -92,13 +92,16 @@ def median_ms(step, B: int, T: int) -> float:
     return statistics.median(a.elapsed_time(b) for a, b in ev)
 
 
-def wake_gpu(dev):
+def wake_gpu(dev, seconds: float = 0.5):
     """Bring the GPU out of its idle clocks before the small cases are timed."""
+    import time
     a = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     b = torch.empty_like(a)
-    for _ in range(20):
-        b.copy_(a)
-    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(20):
+            b.copy_(a)
+        torch.cuda.synchronize()
 
 
 def main(argv=None):
