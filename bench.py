@@ -16,6 +16,8 @@ runs the same per-GPU batch on its own shard of sequences (no data-path collecti
              HBM copy bandwidth of MEASURED_PEAKS.json.
 ``cpu_baseline``: the C restatement of the reference algorithm (oracle/) on the host cores, on a
              bounded sample of the same workload; also used to check the GPU result of the sample.
+             The baseline legs (this one and ``reference_cuda``) are the only code here that touches
+             oracle/, they run after the timed regions, and ``--no-cpu`` skips them.
 ``--impl reference`` times that CPU implementation alone (the reference's torch path cannot travel to
              the GPU box).
 ``reference_cuda``, ``unfused_trio``: for the record, the reference caller's three-call sequence
@@ -454,7 +456,7 @@ def run_encode(args, w, name):
 
     nbytes = algorithmic_bytes(w)
     ref_cuda_leg = None
-    ref = reference_cuda_module(w)
+    ref = None if args.no_cpu else reference_cuda_module(w)     # a baseline leg, like the CPU one
     if ref is not None:
         # the reference's encode kernel (fp16 state), one call per tensor as its caller makes them
         rk, rv = torch.zeros_like(kc), torch.zeros_like(vc)
@@ -606,7 +608,7 @@ def run_ours(args, w, name):
         ms = time_cuda(trio(gemv.forward_qk, gemv.forward_ov, bits=bits, fast=fast, half_state=half), torch, device, n_trio)
         trio_legs["unfused_trio"] = {"ms_per_step": ms, "value": algorithmic_bytes(w) / (ms * 1e-3) / 1e9, "unit": UNIT,
                                      "what": "forward_qk + torch softmax + forward_ov of this library"}
-        ref = reference_cuda_module(w)
+        ref = None if args.no_cpu else reference_cuda_module(w)     # a baseline leg, like the CPU one
         if ref is not None:
             ms = time_cuda(trio(ref.forward_qk, ref.forward_ov), torch, device, n_trio)
             trio_legs["reference_cuda"] = {
@@ -687,7 +689,9 @@ def main():
     ap.add_argument("--ckpt-interval", type=int, default=0,
                     help="decode with state checkpoints every N tokens (segment-parallel kernel + merge)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true",
+                    help="skip the baseline legs, i.e. everything that executes oracle/: the CPU restatement "
+                         "(cpu_baseline, parity_check) and the reference's CUDA kernels (reference_cuda)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
 
