@@ -28,7 +28,9 @@ struct Tile {
 };
 
 // Per-warp bulk-copy ring over the words of one stream.
-template <int BITS, int STAGES = kStages>
+// WIDE = false: head dim 128, the stream is contiguous and its geometry is known at compile time (keeps the
+// 128-wide kernels free of the registers and branches the strided case needs).
+template <int BITS, int STAGES = kStages, bool WIDE = false>
 struct StreamRing {
     uint8_t *buf;           // STAGES * Tile::BYTES, 128-byte aligned
     uint64_t *bar;          // STAGES barriers
@@ -49,7 +51,7 @@ struct StreamRing {
         const int st = i % STAGES;
         const uint32_t bytes = tile_bytes(i);
         mbar_expect_tx(&bar[st], bytes);
-        if (row_stride == kD * 4) {
+        if (!WIDE || row_stride == kD * 4) {
             bulk_load(buf + st * Tile<BITS>::BYTES, src + size_t(i) * Tile<BITS>::BYTES, bytes, &bar[st]);
         } else {   // head_dim > 128: the slice's 512-byte rows are strided, one copy per row
             const uint8_t *row = src + size_t(i) * Tile<BITS>::WORDS * row_stride;
@@ -227,22 +229,23 @@ struct KArgs {
 //   void end_tile(int i, int lane)
 //   void put_self(int g, float v)     lane 0
 //   void finish(int lane)
-template <int BITS, int G, bool EXACT, class Sink, int STAGES = kStages>
+template <int BITS, int G, bool EXACT, class Sink, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, float *red, Sink &sink)
 {
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
-    const int c0 = kD * seg.slice + 4 * lane;      // first of this lane's 4 channels within the head
+    const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
+    const int c0 = kD * slice + 4 * lane;      // first of this lane's 4 channels within the head
     Chan ch[4];
     SafeRange safe;
     FieldConsts<BITS> fc;
     fc.init();
-    load_chan4<BITS, EXACT>(ch, safe, a.p, size_t(h) * a.D + c0, a.smin, a.smax);
-    load_init_state(ch, seg.init, c0, a.D);
+    load_chan4<BITS, EXACT>(ch, safe, a.p, size_t(h) * D + c0, a.smin, a.smax);
+    load_init_state(ch, seg.init, c0, D);
     float qv[G][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * a.D + c0);
+    for (int g = 0; g < G; ++g) load_half4(qv[g], a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * D + c0);
     PairConst pc[2];
     make_pair_consts<EXACT>(ch, pc);
     const f32x2 one = opaque_ones2();   // read once: a constant-memory load per chunk would stall the chain
@@ -253,10 +256,10 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
         qv2[g][1] = pk2(qv[g][2], qv[g][3]);
     }
 
-    const uint32_t row_stride = uint32_t(a.D) * 4;
-    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * a.D + size_t(kD) * seg.slice) * 4;
+    const uint32_t row_stride = uint32_t(D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
     const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS, STAGES> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
                           (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait, row_stride};
     ring.prologue(lane);
 
@@ -313,7 +316,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
     // Append k_new as token T with the state left by token T-1, then its own logit from the
     // dequantised value.
     float xn[4], xh[4];
-    load_half4(xn, a.x_new + size_t(bh) * a.D + c0);
+    load_half4(xn, a.x_new + size_t(bh) * D + c0);
     uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
     uint4 wv = *slot;
     uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -327,7 +330,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
         if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
     }
     *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
-    if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, a.D);
+    if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, D);
     if (!sink.begin_tile(ring.n_tiles)) return;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -439,19 +442,20 @@ struct VArgs {
 //        false = bounded wait gave up
 //   bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
 //   void store(const VArgs&, int b, int h, int c0, const float (&acc)[G][4])   write the result (c0: first channel)
-template <int BITS, int G, bool EXACT, class Src, int STAGES = kStages>
+template <int BITS, int G, bool EXACT, class Src, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, const float2 *wts, Src &src)
 {
     using C = Codec<BITS>;
     const int bh = b * a.Hkv + h;
-    const int c0 = kD * seg.slice + 4 * lane;
+    const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
+    const int c0 = kD * slice + 4 * lane;
     Chan ch[4];
     SafeRange safe;
     FieldConsts<BITS> fc;
     fc.init();
-    load_chan4<BITS, EXACT>(ch, safe, a.p, size_t(h) * a.D + c0, a.smin, a.smax);
-    load_init_state(ch, seg.init, c0, a.D);
+    load_chan4<BITS, EXACT>(ch, safe, a.p, size_t(h) * D + c0, a.smin, a.smax);
+    load_init_state(ch, seg.init, c0, D);
     PairConst pc[2];
     make_pair_consts<EXACT>(ch, pc);
     const f32x2 one = opaque_ones2();   // read once: a constant-memory load per chunk would stall the chain
@@ -461,10 +465,10 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
 
-    const uint32_t row_stride = uint32_t(a.D) * 4;
-    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * a.D + size_t(kD) * seg.slice) * 4;
+    const uint32_t row_stride = uint32_t(D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
     const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS, STAGES> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
                           (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait, row_stride};
     ring.prologue(lane);
 
@@ -513,7 +517,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
         float w_self[G];
         if (!src.self_weight(lane, acc, w_self, a.T)) return;
         float xn[4], xh[4];
-        load_half4(xn, a.x_new + size_t(bh) * a.D + c0);
+        load_half4(xn, a.x_new + size_t(bh) * D + c0);
         uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
         uint4 wv = *slot;
         uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -527,7 +531,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
             if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
         }
         *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
-        if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, a.D);
+        if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, D);
 #pragma unroll
         for (int g = 0; g < G; ++g)
 #pragma unroll

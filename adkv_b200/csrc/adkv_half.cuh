@@ -190,27 +190,28 @@ __device__ __forceinline__ void reduce8_h(const uint32_t *red, int lane, float (
     __syncwarp();
 }
 
-template <int BITS, int G, class Sink, int STAGES = kStages>
+template <int BITS, int G, class Sink, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void k_warp_h(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                          uint64_t *ring_bar, float *red_f, Sink &sink)
 {
     using C = Codec<BITS>;
     uint32_t *red = reinterpret_cast<uint32_t *>(red_f);
     const int bh = b * a.Hkv + h;
-    const int c0 = kD * seg.slice + 4 * lane;
+    const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
+    const int c0 = kD * slice + 4 * lane;
     HPair hp[2];
-    load_pairs(hp, a.p, size_t(h) * a.D + c0);
+    load_pairs(hp, a.p, size_t(h) * D + c0);
     h2 qv[G][2];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const uint2 v = *reinterpret_cast<const uint2 *>(a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * a.D + c0);
+        const uint2 v = *reinterpret_cast<const uint2 *>(a.q + (size_t(b) * a.Hq + size_t(h) * G + g) * D + c0);
         qv[g][0] = v.x;
         qv[g][1] = v.y;
     }
-    const uint32_t row_stride = uint32_t(a.D) * 4;
-    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * a.D + size_t(kD) * seg.slice) * 4;
+    const uint32_t row_stride = uint32_t(D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
     const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS, STAGES> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
                                   (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait, row_stride};
     ring.prologue(lane);
 
@@ -263,7 +264,7 @@ __device__ __forceinline__ void k_warp_h(const KArgs &a, const Seg &seg, int b, 
 
     // Append k_new as token T with the state left by token T-1 (gemv.cu:744-764), then its own logit from the
     // dequantised value (gemv.cu:766-814), accumulated in fp32 here.
-    const uint2 xn = *reinterpret_cast<const uint2 *>(a.x_new + size_t(bh) * a.D + c0);
+    const uint2 xn = *reinterpret_cast<const uint2 *>(a.x_new + size_t(bh) * D + c0);
     const h2 xnp[2] = {xn.x, xn.y};
     uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
     uint4 wv = *slot;
@@ -339,26 +340,27 @@ __device__ __forceinline__ void v_chunk_h(const uint4 &w, HPair (&hp)[2], const 
     }
 }
 
-template <int BITS, int G, class Src, int STAGES = kStages>
+template <int BITS, int G, class Src, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                          uint64_t *ring_bar, const float2 *wts_f2, Src &src)
 {
     using C = Codec<BITS>;
     const uint32_t *wts = reinterpret_cast<const uint32_t *>(wts_f2);   // the source stores fp16 pairs there
     const int bh = b * a.Hkv + h;
-    const int c0 = kD * seg.slice + 4 * lane;
+    const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
+    const int c0 = kD * slice + 4 * lane;
     HPair hp[2];
-    load_pairs(hp, a.p, size_t(h) * a.D + c0);
+    load_pairs(hp, a.p, size_t(h) * D + c0);
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
 
-    const uint32_t row_stride = uint32_t(a.D) * 4;
-    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * a.D + size_t(kD) * seg.slice) * 4;
+    const uint32_t row_stride = uint32_t(D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
     const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS, STAGES> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
                                   (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait, row_stride};
     ring.prologue(lane);
 
@@ -403,7 +405,7 @@ __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, 
     if (seg.append) {   // gemv.cu:1105-1159
         float w_self[G];
         if (!src.self_weight(lane, acc, w_self, a.T)) return;
-        const uint2 xn = *reinterpret_cast<const uint2 *>(a.x_new + size_t(bh) * a.D + c0);
+        const uint2 xn = *reinterpret_cast<const uint2 *>(a.x_new + size_t(bh) * D + c0);
         const h2 xnp[2] = {xn.x, xn.y};
         uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
         uint4 wv = *slot;

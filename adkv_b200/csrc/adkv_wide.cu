@@ -20,16 +20,16 @@ template <int BITS, int G, int MODE, class Sink, int ST>
 __device__ __forceinline__ void k_scan(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
                                        float *red, Sink &sink)
 {
-    if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST>(a, seg, b, h, lane, buf, bar, red, sink);
-    else k_warp<BITS, G, MODE == 1, Sink, ST>(a, seg, b, h, lane, buf, bar, red, sink);
+    if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST, true>(a, seg, b, h, lane, buf, bar, red, sink);
+    else k_warp<BITS, G, MODE == 1, Sink, ST, true>(a, seg, b, h, lane, buf, bar, red, sink);
 }
 
 template <int BITS, int G, int MODE, class Src, int ST>
 __device__ __forceinline__ void v_scan(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
                                        const float2 *wts, Src &src)
 {
-    if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST>(a, seg, b, h, lane, buf, bar, wts, src);
-    else v_warp<BITS, G, MODE == 1, Src, ST>(a, seg, b, h, lane, buf, bar, wts, src);
+    if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST, true>(a, seg, b, h, lane, buf, bar, wts, src);
+    else v_warp<BITS, G, MODE == 1, Src, ST, true>(a, seg, b, h, lane, buf, bar, wts, src);
 }
 
 template <int S>
