@@ -89,7 +89,8 @@ struct EncBatch {
     EncTensor t[2];
 };
 
-template <int BITS>
+// WIDE = false: head dim 128, all strides are compile-time constants.
+template <int BITS, bool WIDE>
 __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, CkptSpec cs, int H, int T,
                                                              int n_super_cap, int t_start, float smin, float smax)
 {
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     const __half *__restrict__ x = et.x;
     const ParamPtrs p = et.p;
     float *__restrict__ tail = et.tail;
-    const int D = cs.D, S = D / kD;
+    const int D = WIDE ? cs.D : kD, S = WIDE ? D / kD : 1;
     const int bh = blockIdx.x / S, h = bh % H, c0 = kD * (blockIdx.x % S) + 2 * threadIdx.x;   // c0: channel in the head
     const size_t po = size_t(h) * D + c0;
     Chan ch[2];
@@ -339,8 +340,13 @@ static int launch_encode(const EncBatch &b, int n, int B, int H, int T, int D, i
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cs.D = D;
     const dim3 grid(B * H * (D / kD), n);
-    if (bits == 4) encode_kernel<4><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
-    else encode_kernel<2><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
+    if (D == kD) {
+        if (bits == 4) encode_kernel<4, false><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
+        else encode_kernel<2, false><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
+    } else {
+        if (bits == 4) encode_kernel<4, true><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
+        else encode_kernel<2, true><<<grid, kEncThreads, 0, s>>>(b, cs, H, T, n_super_cap, t_start, smin, smax);
+    }
     return launch_status();
 }
 

@@ -163,17 +163,18 @@ __device__ __forceinline__ bool encode_group_h(const __half2 *xin /* 8 rows of k
     return doubt;
 }
 
-template <int BITS>
-__global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH batch, int H, int T, int D,
+template <int BITS, bool WIDE>
+__global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH batch, int H, int T, int D_arg,
                                                                    int n_super_cap, int t_start)
 {
+    const int D = WIDE ? D_arg : kD;
     using C = Codec<BITS>;
     const EncTensorH &et = batch.t[blockIdx.y];
     uint32_t *__restrict__ cache = et.cache;
     const __half *__restrict__ x = et.x;
     const ParamPtrs p = et.p;
     float *__restrict__ tail = et.tail;
-    const int S = D / kD;
+    const int S = WIDE ? D / kD : 1;
     const int bh = blockIdx.x / S, h = bh % H, c0 = kD * (blockIdx.x % S) + 2 * threadIdx.x;
     const size_t po = size_t(h) * D + c0;
     const h2 alpha = *reinterpret_cast<const h2 *>(p.alpha + po), beta = *reinterpret_cast<const h2 *>(p.beta + po);
@@ -381,8 +382,13 @@ ADKV_HIDDEN int adkv_half_encode(void *k_cache, const void *k, const adkv_params
     b.t[0] = enc_tensor_h(k_cache, k, kp, k_tail);
     if (n == 2) b.t[1] = enc_tensor_h(v_cache, v, vp, v_tail);
     const dim3 grid(B * H * (D / kD), n);
-    if (bits == 4) encode_half_kernel<4><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
-    else encode_half_kernel<2><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+    if (D == kD) {
+        if (bits == 4) encode_half_kernel<4, false><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+        else encode_half_kernel<2, false><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+    } else {
+        if (bits == 4) encode_half_kernel<4, true><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+        else encode_half_kernel<2, true><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+    }
     return launch_status();
 }
 
