@@ -26,14 +26,7 @@ __global__ void selftest_wait_kernel(unsigned long long limit_ns)
 
 }  // namespace adkv
 
-ADKV_HIDDEN int adkv_tu_status_capi(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, adkv::g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(adkv::g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_capi)
 
 extern "C" {
 

@@ -297,15 +297,7 @@ __global__ void __launch_bounds__(kD) append_kernel(EncBatch batch, CkptSpec cs,
 
 using namespace adkv;
 
-// Status word of this translation unit (read and cleared by adkv_device_status).
-ADKV_HIDDEN int adkv_tu_status_encode(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_encode)
 
 static int encode_check(const void *cache, const void *x, const adkv_params *p, const void *tail, int T, int t_start)
 {

@@ -66,15 +66,7 @@ ADKV_HIDDEN int adkv_half_decode_attn(const KArgs &ka, const VArgs &va, const fl
 ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
                                       float scaling, int B, int bits, int mode, cudaStream_t s);
 
-// Status word of this translation unit (read and cleared by adkv_device_status).
-ADKV_HIDDEN int adkv_tu_status_fused(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_fused)
 
 extern "C" {
 

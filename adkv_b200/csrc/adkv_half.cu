@@ -316,15 +316,7 @@ __global__ void __launch_bounds__(kEncThreadsH) append_half_kernel(EncBatchH bat
 
 using namespace adkv;
 
-// Status word of this translation unit (read and cleared by adkv_device_status).
-ADKV_HIDDEN int adkv_tu_status_half(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_half)
 
 #define ADKV_DISPATCH_H(bits_, G_, CALL)                                              \
     switch ((bits_) * 16 + (G_)) {                                                    \

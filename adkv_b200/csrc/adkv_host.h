@@ -44,6 +44,18 @@ static inline int check_common(int B, int Hq, int Hkv, int T, int D, int n_super
     return 0;
 }
 
+// Every translation unit that includes adkv_device.cuh has its own device status word; this defines the hidden
+// function through which adkv_device_status reads and clears the one of the unit it is expanded in.
+#define ADKV_DEFINE_TU_STATUS(fn_name)                                                \
+    ADKV_HIDDEN int fn_name(int *out)                                                 \
+    {                                                                                 \
+        cudaError_t e = cudaMemcpyFromSymbol(out, adkv::g_status, sizeof(int));       \
+        if (e != cudaSuccess) return int(e);                                          \
+        const int zero = 0;                                                           \
+        e = cudaMemcpyToSymbol(adkv::g_status, &zero, sizeof(int));                   \
+        return e == cudaSuccess ? 0 : int(e);                                         \
+    }
+
 // Dispatch over (bits, group size, arithmetic).
 #define ADKV_DISPATCH_G(BITS_, EXACT_, G_, CALL) \
     switch (G_) {                                \

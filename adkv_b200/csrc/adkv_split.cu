@@ -114,15 +114,7 @@ __global__ void __launch_bounds__(kD) merge_partials_kernel(const float *__restr
 
 using namespace adkv;
 
-// Status word of this translation unit (read and cleared by adkv_device_status).
-ADKV_HIDDEN int adkv_tu_status_split(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_split)
 
 extern "C" {
 

@@ -66,15 +66,7 @@ ADKV_HIDDEN int adkv_half_forward_ov(const VArgs &va, const __half *attn, int B,
 ADKV_HIDDEN int adkv_wide_forward_qk(const KArgs &ka, __half *logits, int B, int bits, int mode, cudaStream_t s);
 ADKV_HIDDEN int adkv_wide_forward_ov(const VArgs &va, const __half *attn, int B, int bits, int mode, cudaStream_t s);
 
-// Status word of this translation unit (read and cleared by adkv_device_status).
-ADKV_HIDDEN int adkv_tu_status_unfused(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_unfused)
 
 extern "C" {
 

@@ -217,15 +217,7 @@ __global__ void __launch_bounds__(32 * S) forward_ov_wide_kernel(VArgs va, const
 
 using namespace adkv;
 
-// Status word of this translation unit (read and cleared by adkv_device_status).
-ADKV_HIDDEN int adkv_tu_status_wide(int *out)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
-    if (e != cudaSuccess) return int(e);
-    const int zero = 0;
-    e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return e == cudaSuccess ? 0 : int(e);
-}
+ADKV_DEFINE_TU_STATUS(adkv_tu_status_wide)
 
 // Called by the public entry points for D = 256 / 512 after argument validation.
 ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
