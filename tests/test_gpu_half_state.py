@@ -308,3 +308,32 @@ def test_wide_heads_equal_reference_kernels(Dw, T):
     f = of.float().cpu().numpy().reshape(B * H, Dw)
     np.testing.assert_allclose(f, a, rtol=3e-2, atol=3e-2 * max(1.0, np.abs(a).max()))
     assert gemv.device_status() == 0
+
+
+@needs_ref
+def test_full_size_config2_equals_reference_kernels():
+    """BASELINE config 2 (batch 128 x 32 heads x 4096 tokens, 4-bit) in the fp16-state arithmetic: the 1 GiB cache
+    our prefill writes, and the codes the fused step appends, are byte for byte what the reference's kernels write."""
+    ref = ref_cuda.module()
+    B, H, T = 128, 32, 4096
+    kp = synth.gen_params(1603, H, D, 4, device="cuda")
+    ns = orc.n_super_for(T + 1, 4)
+    mine = torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    theirs = torch.zeros_like(mine)
+    for b0 in range(0, B, 16):
+        x = synth.gen_kv(1600 + b0, 16, H, T, D, device="cuda")
+        gemv.encode_kv(mine[b0:b0 + 16], x, *kp, SMIN, SMAX, half_state=True)
+        ref.encode_kv(theirs[b0:b0 + 16], x, *kp, SMIN, SMAX)
+        del x
+    assert torch.equal(mine, theirs)
+    q = synth.gen_q(1601, B, H, D, device="cuda")
+    kn = synth.gen_kv(1602, B, H, 1, D, device="cuda", pos0=T)
+    vmine, vtheirs = mine.clone(), theirs.clone()          # the same codes serve as the V cache
+    out = gemv.decode_attn(q, mine, vmine, kn, kn, kp, kp, T, D ** -0.5, SMIN, SMAX, half_state=True)
+    logits = ref.forward_qk(q, theirs, kn, *kp, T, SMIN, SMAX)
+    attn = torch.softmax(logits.float() * D ** -0.5, dim=-1).half()
+    ro = ref.forward_ov(attn, vtheirs, kn, *kp, SMIN, SMAX).reshape(B, H, D)
+    assert torch.equal(mine, theirs) and torch.equal(vmine, vtheirs)
+    a, b = out.float(), ro.float()
+    torch.testing.assert_close(b, a, rtol=3e-2, atol=3e-2 * max(1.0, float(a.abs().max())))
+    assert gemv.device_status() == 0
