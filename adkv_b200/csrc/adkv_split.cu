@@ -96,6 +96,10 @@ __global__ void __launch_bounds__(kD) merge_partials_kernel(const float *__restr
 {
     const int bhq = blockIdx.x, b = bhq / Hq, hq = bhq % Hq, G = Hq / Hkv, h = hq / G, g = hq % G;
     const int c = threadIdx.x;
+    // Launched as a programmatic dependent of the segment kernel (its launch latency is paid while that kernel
+    // still runs): wait here until the segment kernel has completed and its partials are visible.  Without
+    // that launch attribute the instruction does nothing.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const float *base = scratch + (size_t(b * Hkv + h) * n_seg * G + g) * kPartStride;
     const size_t seg_stride = size_t(G) * kPartStride;
     float M = -INFINITY;
@@ -115,6 +119,24 @@ __global__ void __launch_bounds__(kD) merge_partials_kernel(const float *__restr
 using namespace adkv;
 
 ADKV_DEFINE_TU_STATUS(adkv_tu_status_split)
+
+// The merge follows the segment kernel on the same stream as its programmatic dependent: set up early, started
+// when the segment kernel is done (griddepcontrol.wait in the kernel orders the memory).
+static int launch_merge(const float *scratch, __half *out, int B, int Hq, int Hkv, int n_seg, cudaStream_t s)
+{
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(B * Hq);
+    cfg.blockDim = dim3(kD);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, merge_partials_kernel, scratch, out, Hq, Hkv, n_seg);
+    return e == cudaSuccess ? launch_status() : int(e);
+}
 
 extern "C" {
 
@@ -159,9 +181,7 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
                       ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, ck,
                       static_cast<float *>(scratch))))
     if (int rc = launch_status()) return rc;
-    merge_partials_kernel<<<B * Hq, kD, 0, s>>>(static_cast<const float *>(scratch), static_cast<__half *>(out), Hq,
-                                               Hkv, n_seg);
-    return launch_status();
+    return launch_merge(static_cast<const float *>(scratch), static_cast<__half *>(out), B, Hq, Hkv, n_seg, s);
 }
 
 }  // extern "C"
