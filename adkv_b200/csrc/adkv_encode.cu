@@ -13,17 +13,19 @@ constexpr int kEncThreads = kD / 2;
 constexpr int kEncStages = 3;   // 32-token (8 KB) tiles of fp16 input in flight per CTA; 24 KB lets 7+ CTAs share an SM,
                                 // so K and V of 512 streams (1024 CTAs) run as a single wave on 148 SMs
 
-// Eight tokens (fields J0 .. J0+7 of the word being assembled) for the two channels of a thread,
+// Eight tokens for the two channels of a thread,
 // speculative quantiser (see quantize_spec) on the channel pair with packed fp32 arithmetic: half the
 // issue slots for the adds and multiplies, every element rounded exactly as by the scalar instruction.
 // Min/max, the reciprocal and the compare have no packed form and stay scalar.  Returns true when some
 // code is in doubt and the group must be redone with the exactly rounded division.
-template <int BITS, bool GUARDED, int J0>
+// A word is assembled by shifting: every new code enters at the top (one funnel shift takes the low BITS bits of
+// its source) and pushes the earlier tokens down, so after TPW tokens token 0 sits in the lowest field.
+template <int BITS, bool GUARDED>
 __device__ __forceinline__ bool encode_group(const __half2 *xin /* 8 rows of kD/2 */, Chan (&ch)[2],
                                              uint32_t (&word)[2], float smin, float smax, f32x2 one)
 {
     using C = Codec<BITS>;
-    constexpr float M = 12582912.f;   // 1.5 * 2^23
+    constexpr float M = 12582912.f + float(C::BIAS);   // 1.5 * 2^23 + BIAS: the low bits of (v + M) are code + BIAS
     bool doubt = !(ch[0].s < 1e29f) || !(ch[1].s < 1e29f);   // reciprocal would flush to zero
     f32x2 zp = pk2(ch[0].zp, ch[1].zp), s = pk2(ch[0].s, ch[1].s);
     const f32x2 alpha = pk2(ch[0].alpha, ch[1].alpha), beta = pk2(ch[0].beta, ch[1].beta);
@@ -54,8 +56,8 @@ __device__ __forceinline__ bool encode_group(const __half2 *xin /* 8 rows of kD/
         const f32x2 rh = mul2(q, ss);
         uint32_t t0, t1;
         asm("mov.b64 {%0, %1}, %2;" : "=r"(t0), "=r"(t1) : "l"(t));
-        word[0] |= ((t0 & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
-        word[1] |= ((t1 & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
+        word[0] = __funnelshift_r(word[0], t0, BITS);
+        word[1] = __funnelshift_r(word[1], t1, BITS);
         // state update, canonical order (products are added as fma(x, 1, y): see add_product2)
         zp = add_product2(mul2(alpha, rh), one, zp);
         const f32x2 s_new = add_product2(mul2(mul2(s, beta), add2(abs2(q), neg_t)), one, s);
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     constexpr int SRS = kD / 2;    // row stride of the staged slice in shared memory
 
     // one token with a run-time field position, exactly rounded division (partial words, redone groups)
+    // (the word is shifted, not indexed: see encode_group)
     auto exact_token = [&](int t, uint32_t(&word)[2]) {
         const float2 xv = __half22float2(xs[size_t(t - t_start) * RS]);
         const float xa[2] = {xv.x, xv.y};
@@ -146,7 +149,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
         for (int c = 0; c < 2; ++c) {
             float rh;
             const float q = quantize<BITS>(xa[c], ch[c], rh);
-            word[c] |= uint32_t(int(q) + C::BIAS) << (BITS * (t % C::TPW));
+            word[c] = __funnelshift_r(word[c], uint32_t(int(q) + C::BIAS), BITS);
             advance_canonical(q, rh, ch[c], smin, smax);
         }
     };
@@ -168,12 +171,13 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
     const int t_end = t_start + T;
     int t = t_start;
     uint32_t word[2] = {0u, 0u};
-    // a chunk that starts inside a word keeps the fields already there
+    // a chunk that starts inside a word keeps the fields already there (moved to the top, where the shifting
+    // assembly expects the tokens seen so far)
     if (t % C::TPW != 0 && t < t_end) {
         const uint2 old = w[size_t(t / C::TPW) * RS];
-        const uint32_t keep = (1u << (BITS * (t % C::TPW))) - 1u;
-        word[0] = old.x & keep;
-        word[1] = old.y & keep;
+        const int up = BITS * (C::TPW - t % C::TPW);
+        word[0] = old.x << up;
+        word[1] = old.y << up;
     }
     // tokens up to the next multiple of 8
     for (; t < t_end && t % 8 != 0; ++t) {
@@ -218,15 +222,8 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
             const __half2 *rows = reinterpret_cast<const __half2 *>(&buf[i % kEncStages][0]) + g * 8 * SRS + threadIdx.x;
             const Chan saved[2] = {ch[0], ch[1]};
             const uint32_t word_in[2] = {word[0], word[1]};
-            const bool second = C::TPW == 16 && (t & 8);
-            bool doubt;
-            if (safe.holds(ch)) {
-                doubt = second ? encode_group<BITS, false, 8 % C::TPW>(rows, ch, word, smin, smax, one)
-                               : encode_group<BITS, false, 0>(rows, ch, word, smin, smax, one);
-            } else {
-                doubt = second ? encode_group<BITS, true, 8 % C::TPW>(rows, ch, word, smin, smax, one)
-                               : encode_group<BITS, true, 0>(rows, ch, word, smin, smax, one);
-            }
+            const bool doubt = safe.holds(ch) ? encode_group<BITS, false>(rows, ch, word, smin, smax, one)
+                                              : encode_group<BITS, true>(rows, ch, word, smin, smax, one);
             if (doubt) {   // rare, per thread: redo the group from the saved state with the exact quantiser
                 ch[0] = saved[0];
                 ch[1] = saved[1];
@@ -248,7 +245,10 @@ __global__ void __launch_bounds__(kEncThreads) encode_kernel(EncBatch batch, Ckp
         exact_token(t, word);
         checkpoint(t + 1);
     }
-    if (t % C::TPW != 0) w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
+    if (t % C::TPW != 0) {   // bring the tokens of the last, partial word down; its unused fields are zero
+        const int down = BITS * (C::TPW - t % C::TPW);
+        w[size_t(t / C::TPW) * RS] = make_uint2(word[0] >> down, word[1] >> down);
+    }
     if (tail) {
         *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * D + c0) = make_float2(ch[0].zp, ch[1].zp);
         *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * D + D + c0) = make_float2(ch[0].s, ch[1].s);

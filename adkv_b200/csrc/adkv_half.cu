@@ -135,12 +135,13 @@ __device__ __forceinline__ void update_h(h2 q, PairState &s, h2 alpha, h2 beta, 
     s.sc = h2_mul(s.sc, h2_fma(beta, h2_abs(q), omt));
 }
 
-template <int BITS, int J0>
+// (words are assembled by shifting the codes in at the top, as in encode_group of adkv_encode.cu)
+template <int BITS>
 __device__ __forceinline__ bool encode_group_h(const __half2 *xin /* 8 rows of kD/2 */, PairState &st, h2 alpha, h2 beta,
                                                h2 omt, uint32_t (&word)[2])
 {
     using C = Codec<BITS>;
-    constexpr float M = 12582912.f;   // 1.5 * 2^23
+    constexpr float M = 12582912.f + float(C::BIAS);   // 1.5 * 2^23 + BIAS: the low bits of (v + M) are code + BIAS
     bool doubt = false;
     static_for<8>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
@@ -156,8 +157,8 @@ __device__ __forceinline__ bool encode_group_h(const __half2 *xin /* 8 rows of k
         // not finite (zero or infinite scale, NaN) or within 4e-6 of a rounding boundary: redo exactly
         doubt |= !(fabsf(v0) < 1e30f) || !(fabsf(v1) < 1e30f) || !(fabsf(c0 - q0) < 0.5f - 4e-6f) ||
                  !(fabsf(c1 - q1) < 0.5f - 4e-6f);
-        word[0] |= ((__float_as_uint(t0) & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
-        word[1] |= ((__float_as_uint(t1) & C::FIELD) ^ uint32_t(C::BIAS)) << (BITS * (J0 + j));
+        word[0] = __funnelshift_r(word[0], __float_as_uint(t0), BITS);
+        word[1] = __funnelshift_r(word[1], __float_as_uint(t1), BITS);
         update_h(h2_pack(q0, q1), st, alpha, beta, omt);
     });
     return doubt;
@@ -207,8 +208,8 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
         const float2 xv = __half22float2(xs[size_t(t - t_start) * RS]);
         const int q0 = quantize_h<BITS>(xv.x, h2_lo(st.zp), h2_lo(st.sc));
         const int q1 = quantize_h<BITS>(xv.y, h2_hi(st.zp), h2_hi(st.sc));
-        word[0] |= uint32_t(q0 + C::BIAS) << (BITS * (t % C::TPW));
-        word[1] |= uint32_t(q1 + C::BIAS) << (BITS * (t % C::TPW));
+        word[0] = __funnelshift_r(word[0], uint32_t(q0 + C::BIAS), BITS);
+        word[1] = __funnelshift_r(word[1], uint32_t(q1 + C::BIAS), BITS);
         update_h(h2_pack(float(q0), float(q1)), st, alpha, beta, omt);
     };
 
@@ -217,9 +218,9 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
     uint32_t word[2] = {0u, 0u};
     if (t % C::TPW != 0 && t < t_end) {   // a chunk that starts inside a word keeps the fields already there
         const uint2 old = w[size_t(t / C::TPW) * RS];
-        const uint32_t keep = (1u << (BITS * (t % C::TPW))) - 1u;
-        word[0] = old.x & keep;
-        word[1] = old.y & keep;
+        const int up = BITS * (C::TPW - t % C::TPW);
+        word[0] = old.x << up;
+        word[1] = old.y << up;
     }
     for (; t < t_end && t % 8 != 0; ++t) {
         exact_token(t, word);
@@ -258,9 +259,7 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
             const __half2 *rows = reinterpret_cast<const __half2 *>(&buf[i % kEncStagesH][0]) + g * 8 * SRS + threadIdx.x;
             const PairState saved = st;
             const uint32_t word_in[2] = {word[0], word[1]};
-            const bool second = C::TPW == 16 && (t & 8);
-            const bool doubt = second ? encode_group_h<BITS, 8 % C::TPW>(rows, st, alpha, beta, omt, word)
-                                      : encode_group_h<BITS, 0>(rows, st, alpha, beta, omt, word);
+            const bool doubt = encode_group_h<BITS>(rows, st, alpha, beta, omt, word);
             if (doubt) {
                 st = saved;
                 word[0] = word_in[0];
@@ -276,7 +275,10 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
         if (threadIdx.x == 0 && i + kEncStagesH < n_tiles) issue(i + kEncStagesH);
     }
     for (; t < t_end; ++t) exact_token(t, word);
-    if (t % C::TPW != 0) w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
+    if (t % C::TPW != 0) {
+        const int down = BITS * (C::TPW - t % C::TPW);
+        w[size_t(t / C::TPW) * RS] = make_uint2(word[0] >> down, word[1] >> down);
+    }
     if (tail) {
         *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * D + c0) = make_float2(h2_lo(st.zp), h2_hi(st.zp));
         *reinterpret_cast<float2 *>(tail + size_t(bh) * 2 * D + D + c0) = make_float2(h2_lo(st.sc), h2_hi(st.sc));
