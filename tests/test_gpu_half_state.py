@@ -312,7 +312,7 @@ def test_wide_heads_equal_reference_kernels(Dw, T):
 
 @needs_ref
 def test_full_size_config2_equals_reference_kernels():
-    """BASELINE config 2 (batch 128 x 32 heads x 4096 tokens, 4-bit) in the fp16-state arithmetic: the 1 GiB cache
+    """The headline workload (batch 128 x 32 heads x 4096 tokens, 4-bit) in the fp16-state arithmetic: the 1 GiB cache
     our prefill writes, and the codes the fused step appends, are byte for byte what the reference's kernels write."""
     ref = ref_cuda.module()
     B, H, T = 128, 32, 4096
