@@ -30,8 +30,8 @@ SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "adkv_append_kv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
-    "adkv_encode_kv_flags": [c_void_p] * 8 + [c_int] * 7 + [c_float, c_float, c_uint, c_void_p],
-    "adkv_append_kv_flags": [c_void_p] * 8 + [c_int] * 6 + [c_float, c_float, c_uint, c_void_p],
+    "adkv_encode_kv_flags": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_uint, c_void_p],
+    "adkv_append_kv_flags": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_uint, c_void_p],
     "adkv_encode_kv_ckpt": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_void_p],
     "adkv_append_kv_ckpt": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_void_p],
     "adkv_decode_attn_ckpt_scratch_bytes": [c_int, c_int, c_int, c_int, c_int],

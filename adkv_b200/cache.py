@@ -35,8 +35,6 @@ class KVCacheLayer:
             raise ValueError("bits must be 2 or 4")
         if checkpoint_interval and (not capacity_tokens or not fused or checkpoint_interval % 32):
             raise ValueError("checkpoints need a fused cache with capacity_tokens and an interval that is a multiple of 32")
-        if half_state and checkpoint_interval:
-            raise ValueError("state checkpoints belong to the fp32 recurrence (no half_state)")
         self.bits, self.fused, self.fast, self.half_state = bits, fused, fast, half_state
         self._ckpt_interval = checkpoint_interval
         self._kck = self._vck = None

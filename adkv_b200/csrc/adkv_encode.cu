@@ -353,51 +353,68 @@ static int launch_append(const EncBatch &b, int n, int B, int H, int T, int D, i
     return launch_status();
 }
 
-ADKV_HIDDEN int adkv_half_encode(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *v_cache,
-                                 const void *v, const adkv_params *vp, void *v_tail, int n, int B, int H, int T, int D,
-                                 int n_super_cap, int bits, int t_start, cudaStream_t s);
-ADKV_HIDDEN int adkv_half_append(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *v_cache,
-                                 const void *v_new, const adkv_params *vp, void *v_tail, int n, int B, int H, int T,
-                                 int D, int n_super_cap, int bits, cudaStream_t s);
+ADKV_HIDDEN int adkv_half_encode(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                                 void *v_cache, const void *v, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                                 int interval, int n_ckpt_cap, int n, int B, int H, int T, int D, int n_super_cap,
+                                 int bits, int t_start, cudaStream_t s);
+ADKV_HIDDEN int adkv_half_append(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                                 void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                                 int interval, int n_ckpt_cap, int n, int B, int H, int T, int D, int n_super_cap,
+                                 int bits, cudaStream_t s);
 
 extern "C" {
 
-int adkv_encode_kv_flags(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *v_cache,
-                         const void *v, const adkv_params *vp, void *v_tail, int B, int H, int T, int D,
-                         int n_super_cap, int bits, int t_start, float scale_min, float scale_max, unsigned flags,
-                         void *stream)
+int adkv_encode_kv_flags(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                         void *v_cache, const void *v, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                         int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                         int t_start, float scale_min, float scale_max, unsigned flags, void *stream)
 {
     const bool pair = v_cache != nullptr;
-    if (!(flags & ADKV_FLAG_HALF_STATE))
+    if (interval < 0 || (interval > 0 && !pair)) return ADKV_E_SHAPE;   // checkpoints are kept for K and V together
+    if (!(flags & ADKV_FLAG_HALF_STATE)) {
+        if (interval > 0)
+            return adkv_encode_kv_ckpt(k_cache, k, kp, k_tail, k_ckpt, v_cache, v, vp, v_tail, v_ckpt, interval, n_ckpt_cap,
+                                       B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max, stream);
         return pair ? adkv_encode_kv(k_cache, k, kp, k_tail, v_cache, v, vp, v_tail, B, H, T, D, n_super_cap, bits,
                                      t_start, scale_min, scale_max, stream)
                     : adkv_encode(k_cache, k, kp, k_tail, B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max,
                                   stream);
+    }
     if (t_start < 0) return ADKV_E_SHAPE;
     if (int rc = encode_check(k_cache, k, kp, k_tail, T, t_start)) return rc;
     if (pair)
         if (int rc = encode_check(v_cache, v, vp, v_tail, T, t_start)) return rc;
     if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
+    if (interval > 0)
+        if (int rc = ckpt_check(k_ckpt, v_ckpt, interval, n_ckpt_cap, t_start + T)) return rc;
     if (B * H == 0 || (T == 0 && !((k_tail || v_tail) && t_start == 0))) return 0;
-    return adkv_half_encode(k_cache, k, kp, k_tail, v_cache, v, vp, v_tail, pair ? 2 : 1, B, H, T, D, n_super_cap, bits,
-                            t_start, static_cast<cudaStream_t>(stream));
+    return adkv_half_encode(k_cache, k, kp, k_tail, k_ckpt, v_cache, v, vp, v_tail, v_ckpt, interval, n_ckpt_cap,
+                            pair ? 2 : 1, B, H, T, D, n_super_cap, bits, t_start, static_cast<cudaStream_t>(stream));
 }
 
-int adkv_append_kv_flags(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *v_cache,
-                         const void *v_new, const adkv_params *vp, void *v_tail, int B, int H, int T, int D,
-                         int n_super_cap, int bits, float scale_min, float scale_max, unsigned flags, void *stream)
+int adkv_append_kv_flags(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                         void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                         int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                         float scale_min, float scale_max, unsigned flags, void *stream)
 {
     const bool pair = v_cache != nullptr;
-    if (!(flags & ADKV_FLAG_HALF_STATE))
+    if (interval < 0 || (interval > 0 && !pair)) return ADKV_E_SHAPE;
+    if (!(flags & ADKV_FLAG_HALF_STATE)) {
+        if (interval > 0)
+            return adkv_append_kv_ckpt(k_cache, k_new, kp, k_tail, k_ckpt, v_cache, v_new, vp, v_tail, v_ckpt, interval,
+                                       n_ckpt_cap, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream);
         return pair ? adkv_append_kv(k_cache, k_new, kp, k_tail, v_cache, v_new, vp, v_tail, B, H, T, D, n_super_cap,
                                      bits, scale_min, scale_max, stream)
                     : adkv_append(k_cache, k_new, kp, k_tail, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream);
+    }
     if (!k_cache || !k_new || !k_tail || !params_ok(kp)) return ADKV_E_NULL;
     if (pair && (!v_new || !v_tail || !params_ok(vp))) return ADKV_E_NULL;
     if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (interval > 0)
+        if (int rc = ckpt_check(k_ckpt, v_ckpt, interval, n_ckpt_cap, T + 1)) return rc;
     if (B * H == 0) return 0;
-    return adkv_half_append(k_cache, k_new, kp, k_tail, v_cache, v_new, vp, v_tail, pair ? 2 : 1, B, H, T, D,
-                            n_super_cap, bits, static_cast<cudaStream_t>(stream));
+    return adkv_half_append(k_cache, k_new, kp, k_tail, k_ckpt, v_cache, v_new, vp, v_tail, v_ckpt, interval, n_ckpt_cap,
+                            pair ? 2 : 1, B, H, T, D, n_super_cap, bits, static_cast<cudaStream_t>(stream));
 }
 
 int adkv_encode(void *cache, const void *x, const adkv_params *p, void *tail, int B, int H, int T, int D,

@@ -120,6 +120,11 @@ struct EncTensorH {
     const __half *x;
     ParamPtrs p;
     float *tail;   // [B, H, 2, D] float holding fp16-representable values, or nullptr
+    float *ckpt;   // state checkpoints [B*H][n_ckpt_cap][2][D] (same convention as the fp32 kernels) or nullptr
+};
+struct CkptSpecH {
+    int interval;     // tokens between checkpoints (multiple of 32), 0 = none
+    int n_ckpt_cap;
 };
 struct EncBatchH {
     EncTensorH t[2];
@@ -165,7 +170,7 @@ __device__ __forceinline__ bool encode_group_h(const __half2 *xin /* 8 rows of k
 }
 
 template <int BITS, bool WIDE>
-__global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH batch, int H, int T, int D_arg,
+__global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH batch, CkptSpecH cs, int H, int T, int D_arg,
                                                                    int n_super_cap, int t_start)
 {
     const int D = WIDE ? D_arg : kD;
@@ -213,6 +218,20 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
         update_h(h2_pack(float(q0), float(q1)), st, alpha, beta, omt);
     };
 
+    // checkpoint k is written when the state before token (k+1)*interval is reached
+    float *ckpt = (et.ckpt && cs.interval > 0) ? et.ckpt + size_t(bh) * cs.n_ckpt_cap * 2 * D + c0 : nullptr;
+    int next_ckpt = ckpt ? (t_start / cs.interval + 1) * cs.interval : 0x7fffffff;
+    auto checkpoint = [&](int t_reached) {
+        if (t_reached == next_ckpt) {
+            const int k = next_ckpt / cs.interval - 1;
+            if (k < cs.n_ckpt_cap) {
+                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * D) = make_float2(h2_lo(st.zp), h2_hi(st.zp));
+                *reinterpret_cast<float2 *>(ckpt + size_t(k) * 2 * D + D) = make_float2(h2_lo(st.sc), h2_hi(st.sc));
+            }
+            next_ckpt += cs.interval;
+        }
+    };
+
     const int t_end = t_start + T;
     int t = t_start;
     uint32_t word[2] = {0u, 0u};
@@ -224,6 +243,7 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
     }
     for (; t < t_end && t % 8 != 0; ++t) {
         exact_token(t, word);
+        checkpoint(t + 1);
         if ((t + 1) % C::TPW == 0) {
             w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
             word[0] = word[1] = 0u;
@@ -266,6 +286,7 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
                 word[1] = word_in[1];
                 for (int j = 0; j < 8; ++j) exact_token(t + j, word);
             }
+            checkpoint(t + 8);
             if ((t + 8) % C::TPW == 0) {
                 w[size_t(t / C::TPW) * RS] = make_uint2(word[0], word[1]);
                 word[0] = word[1] = 0u;
@@ -274,7 +295,10 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
         __syncthreads();
         if (threadIdx.x == 0 && i + kEncStagesH < n_tiles) issue(i + kEncStagesH);
     }
-    for (; t < t_end; ++t) exact_token(t, word);
+    for (; t < t_end; ++t) {
+        exact_token(t, word);
+        checkpoint(t + 1);
+    }
     if (t % C::TPW != 0) {
         const int down = BITS * (C::TPW - t % C::TPW);
         w[size_t(t / C::TPW) * RS] = make_uint2(word[0] >> down, word[1] >> down);
@@ -287,7 +311,8 @@ __global__ void __launch_bounds__(kEncThreadsH) encode_half_kernel(EncBatchH bat
 
 // Single-token append from the persisted tail state (gemv.cu:91-146 without the replay that precedes it there).
 template <int BITS>
-__global__ void __launch_bounds__(kEncThreadsH) append_half_kernel(EncBatchH batch, int H, int T, int D, int n_super_cap)
+__global__ void __launch_bounds__(kEncThreadsH) append_half_kernel(EncBatchH batch, CkptSpecH cs, int H, int T, int D,
+                                                                   int n_super_cap)
 {
     using C = Codec<BITS>;
     const EncTensorH &et = batch.t[blockIdx.y];
@@ -312,6 +337,14 @@ __global__ void __launch_bounds__(kEncThreadsH) append_half_kernel(EncBatchH bat
     update_h(h2_pack(float(q0), float(q1)), st, alpha, beta, omt);
     *tz = make_float2(h2_lo(st.zp), h2_hi(st.zp));
     *ts = make_float2(h2_lo(st.sc), h2_hi(st.sc));
+    if (et.ckpt && cs.interval > 0 && (T + 1) % cs.interval == 0) {
+        const int k = (T + 1) / cs.interval - 1;
+        if (k < cs.n_ckpt_cap) {
+            float *dst = et.ckpt + (size_t(bh) * cs.n_ckpt_cap + k) * 2 * D + c0;
+            *reinterpret_cast<float2 *>(dst) = *tz;
+            *reinterpret_cast<float2 *>(dst + D) = *ts;
+        }
+    }
 }
 
 }  // namespace adkv
@@ -319,19 +352,6 @@ __global__ void __launch_bounds__(kEncThreadsH) append_half_kernel(EncBatchH bat
 using namespace adkv;
 
 ADKV_DEFINE_TU_STATUS(adkv_tu_status_half)
-
-#define ADKV_DISPATCH_H(bits_, G_, CALL)                                              \
-    switch ((bits_) * 16 + (G_)) {                                                    \
-    case 4 * 16 + 1: { constexpr int BITS = 4; constexpr int G = 1; CALL; } break;    \
-    case 4 * 16 + 2: { constexpr int BITS = 4; constexpr int G = 2; CALL; } break;    \
-    case 4 * 16 + 4: { constexpr int BITS = 4; constexpr int G = 4; CALL; } break;    \
-    case 4 * 16 + 8: { constexpr int BITS = 4; constexpr int G = 8; CALL; } break;    \
-    case 2 * 16 + 1: { constexpr int BITS = 2; constexpr int G = 1; CALL; } break;    \
-    case 2 * 16 + 2: { constexpr int BITS = 2; constexpr int G = 2; CALL; } break;    \
-    case 2 * 16 + 4: { constexpr int BITS = 2; constexpr int G = 4; CALL; } break;    \
-    case 2 * 16 + 8: { constexpr int BITS = 2; constexpr int G = 8; CALL; } break;    \
-    default: return ADKV_E_SHAPE;                                                     \
-    }
 
 ADKV_HIDDEN int adkv_half_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
                                       float scaling, int B, int bits, const int *seq_lens, cudaStream_t s)
@@ -361,40 +381,44 @@ ADKV_HIDDEN int adkv_half_forward_ov(const VArgs &va, const __half *attn, int B,
     return launch_status();
 }
 
-static EncTensorH enc_tensor_h(void *cache, const void *x, const adkv_params *p, void *tail)
+static EncTensorH enc_tensor_h(void *cache, const void *x, const adkv_params *p, void *tail, void *ckpt)
 {
     return EncTensorH{static_cast<uint32_t *>(cache), static_cast<const __half *>(x), to_ptrs(p),
-                      static_cast<float *>(tail)};
+                      static_cast<float *>(tail), static_cast<float *>(ckpt)};
 }
 
 // n tensors (1 or 2) of one layer; arguments already validated by the caller.
-ADKV_HIDDEN int adkv_half_encode(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *v_cache,
-                                 const void *v, const adkv_params *vp, void *v_tail, int n, int B, int H, int T, int D,
-                                 int n_super_cap, int bits, int t_start, cudaStream_t s)
+ADKV_HIDDEN int adkv_half_encode(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                                 void *v_cache, const void *v, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                                 int interval, int n_ckpt_cap, int n, int B, int H, int T, int D, int n_super_cap,
+                                 int bits, int t_start, cudaStream_t s)
 {
     EncBatchH b{};
-    b.t[0] = enc_tensor_h(k_cache, k, kp, k_tail);
-    if (n == 2) b.t[1] = enc_tensor_h(v_cache, v, vp, v_tail);
+    b.t[0] = enc_tensor_h(k_cache, k, kp, k_tail, k_ckpt);
+    if (n == 2) b.t[1] = enc_tensor_h(v_cache, v, vp, v_tail, v_ckpt);
+    const CkptSpecH cs{interval, n_ckpt_cap};
     const dim3 grid(B * H * (D / kD), n);
     if (D == kD) {
-        if (bits == 4) encode_half_kernel<4, false><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
-        else encode_half_kernel<2, false><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+        if (bits == 4) encode_half_kernel<4, false><<<grid, kEncThreadsH, 0, s>>>(b, cs, H, T, D, n_super_cap, t_start);
+        else encode_half_kernel<2, false><<<grid, kEncThreadsH, 0, s>>>(b, cs, H, T, D, n_super_cap, t_start);
     } else {
-        if (bits == 4) encode_half_kernel<4, true><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
-        else encode_half_kernel<2, true><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap, t_start);
+        if (bits == 4) encode_half_kernel<4, true><<<grid, kEncThreadsH, 0, s>>>(b, cs, H, T, D, n_super_cap, t_start);
+        else encode_half_kernel<2, true><<<grid, kEncThreadsH, 0, s>>>(b, cs, H, T, D, n_super_cap, t_start);
     }
     return launch_status();
 }
 
-ADKV_HIDDEN int adkv_half_append(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *v_cache,
-                                 const void *v_new, const adkv_params *vp, void *v_tail, int n, int B, int H, int T,
-                                 int D, int n_super_cap, int bits, cudaStream_t s)
+ADKV_HIDDEN int adkv_half_append(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                                 void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                                 int interval, int n_ckpt_cap, int n, int B, int H, int T, int D, int n_super_cap,
+                                 int bits, cudaStream_t s)
 {
     EncBatchH b{};
-    b.t[0] = enc_tensor_h(k_cache, k_new, kp, k_tail);
-    if (n == 2) b.t[1] = enc_tensor_h(v_cache, v_new, vp, v_tail);
+    b.t[0] = enc_tensor_h(k_cache, k_new, kp, k_tail, k_ckpt);
+    if (n == 2) b.t[1] = enc_tensor_h(v_cache, v_new, vp, v_tail, v_ckpt);
+    const CkptSpecH cs{interval, n_ckpt_cap};
     const dim3 grid(B * H * (D / kD), n);
-    if (bits == 4) append_half_kernel<4><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap);
-    else append_half_kernel<2><<<grid, kEncThreadsH, 0, s>>>(b, H, T, D, n_super_cap);
+    if (bits == 4) append_half_kernel<4><<<grid, kEncThreadsH, 0, s>>>(b, cs, H, T, D, n_super_cap);
+    else append_half_kernel<2><<<grid, kEncThreadsH, 0, s>>>(b, cs, H, T, D, n_super_cap);
     return launch_status();
 }

@@ -88,6 +88,32 @@ __device__ __forceinline__ void load_pairs(HPair (&hp)[2], const ParamPtrs &p, s
     hp[1] = HPair{a.y, b.y, c.y, d.y, h2_fma(h2_neg(d.y), e.y, kOne2)};
 }
 
+// State update alone (after an appended token).
+__device__ __forceinline__ void advance_h(h2 q, HPair &c)
+{
+    c.zp = h2_fma(c.alpha, h2_mul(q, c.sc), c.zp);
+    c.sc = h2_mul(c.sc, h2_fma(c.beta, h2_abs(q), c.omt));
+}
+
+// Checkpointed states are stored as float [2][head_dim] (zp, scale) in both arithmetics; fp16 values pass
+// through float exactly in either direction.
+__device__ __forceinline__ void load_init_state_h(HPair (&hp)[2], const float *init, int c0, int D)
+{
+    if (init) {
+        const float4 zp = *reinterpret_cast<const float4 *>(init + c0);
+        const float4 sc = *reinterpret_cast<const float4 *>(init + D + c0);
+        hp[0].zp = h2_pack(zp.x, zp.y); hp[1].zp = h2_pack(zp.z, zp.w);
+        hp[0].sc = h2_pack(sc.x, sc.y); hp[1].sc = h2_pack(sc.z, sc.w);
+    }
+}
+
+__device__ __forceinline__ void store_state_h(float *dst, const HPair (&hp)[2], int c0, int D)
+{
+    *reinterpret_cast<float4 *>(dst + c0) = make_float4(h2_lo(hp[0].zp), h2_hi(hp[0].zp), h2_lo(hp[1].zp), h2_hi(hp[1].zp));
+    *reinterpret_cast<float4 *>(dst + D + c0) =
+        make_float4(h2_lo(hp[0].sc), h2_hi(hp[0].sc), h2_lo(hp[1].sc), h2_hi(hp[1].sc));
+}
+
 // One token of a channel pair: dequantised values (q * sc + zp with the state BEFORE the token), then the update.
 __device__ __forceinline__ h2 step_h(h2 q, HPair &c)
 {
@@ -201,6 +227,7 @@ __device__ __forceinline__ void k_warp_h(const KArgs &a, const Seg &seg, int b, 
     const int c0 = kD * slice + 4 * lane;
     HPair hp[2];
     load_pairs(hp, a.p, size_t(h) * D + c0);
+    load_init_state_h(hp, seg.init, c0, D);
     h2 qv[G][2];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -277,11 +304,14 @@ __device__ __forceinline__ void k_warp_h(const KArgs &a, const Seg &seg, int b, 
         const int q1 = quantize_h<BITS>(h2_hi(xnp[p]), h2_hi(hp[p].zp), h2_hi(hp[p].sc));
         ww[2 * p] = (ww[2 * p] & ~(C::FIELD << sh)) | (uint32_t(q0 + C::BIAS) << sh);
         ww[2 * p + 1] = (ww[2 * p + 1] & ~(C::FIELD << sh)) | (uint32_t(q1 + C::BIAS) << sh);
-        const h2 deq = h2_fma(h2_pack(float(q0), float(q1)), hp[p].sc, hp[p].zp);
+        const h2 qf = h2_pack(float(q0), float(q1));
+        const h2 deq = h2_fma(qf, hp[p].sc, hp[p].zp);
         xh[2 * p] = h2_lo(deq);
         xh[2 * p + 1] = h2_hi(deq);
+        if (seg.ckpt_out) advance_h(qf, hp[p]);
     }
     *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+    if (seg.ckpt_out) store_state_h(seg.ckpt_out, hp, c0, D);
     if (!sink.begin_tile(ring.n_tiles)) return;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -351,6 +381,7 @@ __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, 
     const int c0 = kD * slice + 4 * lane;
     HPair hp[2];
     load_pairs(hp, a.p, size_t(h) * D + c0);
+    load_init_state_h(hp, seg.init, c0, D);
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -417,16 +448,39 @@ __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, 
             const int q1 = quantize_h<BITS>(h2_hi(xnp[p]), h2_hi(hp[p].zp), h2_hi(hp[p].sc));
             ww[2 * p] = (ww[2 * p] & ~(C::FIELD << sh)) | (uint32_t(q0 + C::BIAS) << sh);
             ww[2 * p + 1] = (ww[2 * p + 1] & ~(C::FIELD << sh)) | (uint32_t(q1 + C::BIAS) << sh);
-            const h2 deq = h2_fma(h2_pack(float(q0), float(q1)), hp[p].sc, hp[p].zp);
+            const h2 qf = h2_pack(float(q0), float(q1));
+            const h2 deq = h2_fma(qf, hp[p].sc, hp[p].zp);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 acc[g][2 * p] = fmaf(w_self[g], h2_lo(deq), acc[g][2 * p]);
                 acc[g][2 * p + 1] = fmaf(w_self[g], h2_hi(deq), acc[g][2 * p + 1]);
             }
+            if (seg.ckpt_out) advance_h(qf, hp[p]);
         }
         *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+        if (seg.ckpt_out) store_state_h(seg.ckpt_out, hp, c0, D);
     }
     src.store(a, b, h, c0, acc);
+}
+
+// Scan of one tensor of a stream in the arithmetic MODE selects: 0 = fp32 recurrence, contracted replay;
+// 1 = fp32 recurrence, canonical order; 2 = the fp16-state arithmetic above.
+constexpr int kModeHalf = 2;
+
+template <int BITS, int G, int MODE, class Sink, int ST = kStages, bool WIDE = false>
+__device__ __forceinline__ void k_scan(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
+                                       float *red, Sink &sink)
+{
+    if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
+    else k_warp<BITS, G, MODE == 1, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
+}
+
+template <int BITS, int G, int MODE, class Src, int ST = kStages, bool WIDE = false>
+__device__ __forceinline__ void v_scan(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
+                                       const float2 *wts, Src &src)
+{
+    if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
+    else v_warp<BITS, G, MODE == 1, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
 }
 
 }  // namespace adkv

@@ -73,4 +73,18 @@ static inline int check_common(int B, int Hq, int Hkv, int T, int D, int n_super
     }
 
 
+// Dispatch over (bits, group size) for kernels without an EXACT parameter.
+#define ADKV_DISPATCH_H(bits_, G_, CALL)                                              \
+    switch ((bits_) * 16 + (G_)) {                                                    \
+    case 4 * 16 + 1: { constexpr int BITS = 4; constexpr int G = 1; CALL; } break;    \
+    case 4 * 16 + 2: { constexpr int BITS = 4; constexpr int G = 2; CALL; } break;    \
+    case 4 * 16 + 4: { constexpr int BITS = 4; constexpr int G = 4; CALL; } break;    \
+    case 4 * 16 + 8: { constexpr int BITS = 4; constexpr int G = 8; CALL; } break;    \
+    case 2 * 16 + 1: { constexpr int BITS = 2; constexpr int G = 1; CALL; } break;    \
+    case 2 * 16 + 2: { constexpr int BITS = 2; constexpr int G = 2; CALL; } break;    \
+    case 2 * 16 + 4: { constexpr int BITS = 2; constexpr int G = 4; CALL; } break;    \
+    case 2 * 16 + 8: { constexpr int BITS = 2; constexpr int G = 8; CALL; } break;    \
+    default: return ADKV_E_SHAPE;                                                     \
+    }
+
 }  // namespace adkv

@@ -10,14 +10,15 @@
 
 #include <mutex>
 
+#include "adkv_half.cuh"
 #include "adkv_softmax.cuh"
 
 namespace adkv {
 
 constexpr int kPartStride = 4 + kD;   // floats per (stream, segment, head): max (log2 units), denominator, 2 pad, kD sums
 
-template <int G>
-struct PartialSrc : SoftmaxSrc<G> {
+template <int G, bool HALF_W>
+struct PartialSrc : SoftmaxSrc<G, 1, HALF_W> {
     float *part;   // [G][kPartStride] of this (stream, segment)
     __device__ __forceinline__ void store(const VArgs &, int, int, int c0, const float (&acc)[G][4]) const
     {
@@ -38,7 +39,7 @@ struct CkptArgs {
     int interval, n_ckpt_cap;
 };
 
-template <int BITS, int G, bool EXACT>
+template <int BITS, int G, int MODE>
 __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
                                                                long long mask_stride_b, float scaling, CkptArgs ck,
                                                                float *__restrict__ scratch)
@@ -73,11 +74,11 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
         seg.init = j ? ck.k_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
         seg.ckpt_out = write_ckpt ? ck.k_ckpt + out_idx * 2 * kD : nullptr;
         RingSink<G> sink{&fs, 0, 0};
-        k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
+        k_scan<BITS, G, MODE>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         seg.init = j ? ck.v_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
         seg.ckpt_out = write_ckpt ? ck.v_ckpt + out_idx * 2 * kD : nullptr;
-        PartialSrc<G> src;
+        PartialSrc<G, MODE == kModeHalf> src;
         src.sh = &fs;
         src.wts = wts;
         src.mask = mask ? mask + size_t(b) * mask_stride_b : nullptr;
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
         src.t_begin = seg.t_begin;
         src.part = scratch + (size_t(bh) * n_seg + j) * G * kPartStride;
         src.init();
-        v_warp<BITS, G, EXACT>(va, seg, b, h, lane, vbuf, vbar, wts, src);
+        v_scan<BITS, G, MODE>(va, seg, b, h, lane, vbuf, vbar, wts, src);
     }
 }
 
@@ -171,15 +172,21 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
                    to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
     const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ADKV_FLAG_HALF_STATE) return ADKV_E_FLAGS;   // checkpoints hold fp32 states of the fp32 recurrence
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     const int n_seg = T / interval + 1;
     if (n_seg > 65535) return ADKV_E_SHAPE;
     const dim3 grid(B * Hkv, n_seg);
-    ADKV_DISPATCH(bits, exact, Hq / Hkv,
-                  (decode_attn_split_kernel<BITS, G, EXACT><<<grid, 64, 0, s>>>(
-                      ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, ck,
-                      static_cast<float *>(scratch))))
+    if (flags & ADKV_FLAG_HALF_STATE) {
+        ADKV_DISPATCH_H(bits, Hq / Hkv,
+                        (decode_attn_split_kernel<BITS, G, kModeHalf><<<grid, 64, 0, s>>>(
+                          ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, ck,
+                          static_cast<float *>(scratch))))
+    } else {
+        ADKV_DISPATCH(bits, exact, Hq / Hkv,
+                      (decode_attn_split_kernel<BITS, G, int(EXACT)><<<grid, 64, 0, s>>>(
+                          ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, ck,
+                          static_cast<float *>(scratch))))
+    }
     if (int rc = launch_status()) return rc;
     return launch_merge(static_cast<const float *>(scratch), static_cast<__half *>(out), B, Hq, Hkv, n_seg, s);
 }

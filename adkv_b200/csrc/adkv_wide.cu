@@ -12,26 +12,6 @@
 
 namespace adkv {
 
-// MODE: 0 = fp32 recurrence, contracted replay; 1 = fp32 recurrence, canonical order; 2 = the fp16-state
-// arithmetic of the reference's kernels (adkv_half.cuh).
-constexpr int kModeHalf = 2;
-
-template <int BITS, int G, int MODE, class Sink, int ST>
-__device__ __forceinline__ void k_scan(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
-                                       float *red, Sink &sink)
-{
-    if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST, true>(a, seg, b, h, lane, buf, bar, red, sink);
-    else k_warp<BITS, G, MODE == 1, Sink, ST, true>(a, seg, b, h, lane, buf, bar, red, sink);
-}
-
-template <int BITS, int G, int MODE, class Src, int ST>
-__device__ __forceinline__ void v_scan(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
-                                       const float2 *wts, Src &src)
-{
-    if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST, true>(a, seg, b, h, lane, buf, bar, wts, src);
-    else v_warp<BITS, G, MODE == 1, Src, ST, true>(a, seg, b, h, lane, buf, bar, wts, src);
-}
-
 template <int S>
 struct WideCfg {
     static constexpr int STAGES = S >= 4 ? 2 : 3;   // keeps the static shared memory of 2*S rings under 48 KB
@@ -63,7 +43,7 @@ __global__ void __launch_bounds__(64 * S) decode_attn_wide_kernel(KArgs ka, VArg
     const Seg seg{0, ka.T, true, nullptr, nullptr, sl};
     if (role == 0) {
         RingSink<G, S> sink{&fs, 0, sl};
-        k_scan<BITS, G, MODE, RingSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
+        k_scan<BITS, G, MODE, RingSink<G, S>, ST, true>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
     } else {
         SoftmaxSrc<G, S, MODE == kModeHalf> src;
         src.sh = &fs;
@@ -73,7 +53,7 @@ __global__ void __launch_bounds__(64 * S) decode_attn_wide_kernel(KArgs ka, VArg
         src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
         src.t_begin = 0;
         src.init();
-        v_scan<BITS, G, MODE, SoftmaxSrc<G, S, MODE == kModeHalf>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl],
+        v_scan<BITS, G, MODE, SoftmaxSrc<G, S, MODE == kModeHalf>, ST, true>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl],
                                                                        src);
     }
 }
@@ -140,10 +120,10 @@ __global__ void __launch_bounds__(32 * S) forward_qk_wide_kernel(KArgs ka, __hal
         sink.T = ka.T;
 #pragma unroll
         for (int g = 0; g < G; ++g) sink.row[g] = logits + (size_t(b) * ka.Hq + size_t(h) * G + g) * (ka.T + 1);
-        k_scan<BITS, G, MODE, WriterSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[0], kbar[0], red[0], sink);
+        k_scan<BITS, G, MODE, WriterSink<G, S>, ST, true>(ka, seg, b, h, lane, kbuf[0], kbar[0], red[0], sink);
     } else {
         RingSink<G, S> sink{&fs, 0, sl};
-        k_scan<BITS, G, MODE, RingSink<G, S>, ST>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
+        k_scan<BITS, G, MODE, RingSink<G, S>, ST, true>(ka, seg, b, h, lane, kbuf[sl], kbar[sl], red[sl], sink);
     }
 }
 
@@ -194,7 +174,7 @@ __global__ void __launch_bounds__(32 * S) forward_ov_wide_kernel(VArgs va, const
     for (int g = 0; g < G; ++g) src.row[g] = attn + (size_t(b) * va.Hq + size_t(h) * G + g) * (va.T + 1);
     src.wts = wts[sl];
     const Seg seg{0, va.T, true, nullptr, nullptr, sl};
-    v_scan<BITS, G, MODE, WideWeightSrc<G, MODE == kModeHalf>, ST>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
+    v_scan<BITS, G, MODE, WideWeightSrc<G, MODE == kModeHalf>, ST, true>(va, seg, b, h, lane, vbuf[sl], vbar[sl], wts[sl], src);
 }
 
 // Dispatch over (bits, arithmetic, slices, group size); group sizes are limited by the 48 KB of static shared memory.

@@ -130,8 +130,8 @@ def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min
         if half_state:
             rc = _lib.load().adkv_encode_kv_flags(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
                                                   None if tail is None else tail.data_ptr(), None, None, None, None,
-                                                  B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max,
-                                                  _lib.FLAG_HALF_STATE, _stream(kv_cache))
+                                                  None, None, 0, 0, B, H, T, D, n_super_cap, bits, t_start, scale_min,
+                                                  scale_max, _lib.FLAG_HALF_STATE, _stream(kv_cache))
         else:
             rc = _lib.load().adkv_encode(kv_cache.data_ptr(), x.data_ptr(), ctypes.addressof(p),
                                          None if tail is None else tail.data_ptr(), B, H, T, D, n_super_cap, bits,
@@ -191,13 +191,13 @@ def encode_kv_pair(k_cache, k_new, k_params, v_cache, v_new, v_params, scale_min
     kp, keep_k = _params(names, tuple(k_params), H, D, k_cache.device)
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
-    _require(not (half_state and ckpt_interval), "state checkpoints belong to the fp32 recurrence (no half_state)")
     with _on_device(k_cache.device):
         if half_state:
+            kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D) if ckpt_interval else (None, None, 0, 0)
             rc = _lib.load().adkv_encode_kv_flags(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
-                                                  _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
-                                                  ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D,
-                                                  n_super_cap, bits, t_start, scale_min, scale_max,
+                                                  _tail_ptr(k_tail, B, H, D), kc, v_cache.data_ptr(), xv.data_ptr(),
+                                                  ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), vc, iv, cap, B, H, T,
+                                                  D, n_super_cap, bits, t_start, scale_min, scale_max,
                                                   _lib.FLAG_HALF_STATE, _stream(k_cache))
         elif ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D)
@@ -231,13 +231,13 @@ def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v
     kp, keep_k = _params(names, tuple(k_params), H, D, k_cache.device)
     vp, keep_v = _params(names, tuple(v_params), H, D, k_cache.device)
     xk, xv = k_new.contiguous(), v_new.contiguous()
-    _require(not (half_state and ckpt_interval), "state checkpoints belong to the fp32 recurrence (no half_state)")
     with _on_device(k_cache.device):
         if half_state:
+            kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D) if ckpt_interval else (None, None, 0, 0)
             rc = _lib.load().adkv_append_kv_flags(k_cache.data_ptr(), xk.data_ptr(), ctypes.addressof(kp),
-                                                  _tail_ptr(k_tail, B, H, D), v_cache.data_ptr(), xv.data_ptr(),
-                                                  ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), B, H, T, D,
-                                                  n_super_cap, bits, scale_min, scale_max, _lib.FLAG_HALF_STATE,
+                                                  _tail_ptr(k_tail, B, H, D), kc, v_cache.data_ptr(), xv.data_ptr(),
+                                                  ctypes.addressof(vp), _tail_ptr(v_tail, B, H, D), vc, iv, cap, B, H, T,
+                                                  D, n_super_cap, bits, scale_min, scale_max, _lib.FLAG_HALF_STATE,
                                                   _stream(k_cache))
         elif ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, H, D)
@@ -272,8 +272,8 @@ def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min
     with _on_device(cache.device):
         if half_state:
             rc = _lib.load().adkv_append_kv_flags(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
-                                                  None, None, None, None, B, H, T, D, n_super_cap, bits, scale_min,
-                                                  scale_max, _lib.FLAG_HALF_STATE, _stream(cache))
+                                                  None, None, None, None, None, None, 0, 0, B, H, T, D, n_super_cap,
+                                                  bits, scale_min, scale_max, _lib.FLAG_HALF_STATE, _stream(cache))
         else:
             rc = _lib.load().adkv_append(cache.data_ptr(), x.data_ptr(), ctypes.addressof(p), tail.data_ptr(),
                                          B, H, T, D, n_super_cap, bits, scale_min, scale_max, _stream(cache))

@@ -46,7 +46,7 @@ extern "C" {
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
 #define ADKV_E_SCRATCH   (-8)  /* the scratch memory given is smaller than the problem needs */
 #define ADKV_E_STATIC_MAX (-9) /* problem needs more than ADKV_STATIC_SCRATCH_BYTES of built-in scratch */
-#define ADKV_E_FLAGS     (-10) /* ADKV_FLAG_HALF_STATE is not available for this entry point */
+#define ADKV_E_FLAGS     (-10) /* a flag is not available for this entry point (none at present) */
 
 /* Size of the library's built-in scratch array (see adkv_decode_attn_ckpt_static). */
 #define ADKV_STATIC_SCRATCH_BYTES (16u << 20)
@@ -59,8 +59,8 @@ extern "C" {
  * (src/adkv/kernel/gemv.cu:150-164).  Codes, appended codes and tail states are bit-identical to what the
  * reference's encode_kv / forward_qk / forward_ov produce, so caches can be exchanged with them; logits and
  * outputs are accumulated more accurately than there (fp32 across tokens) and agree within fp16 accumulation
- * error.  Takes precedence over ADKV_FLAG_FAST_REPLAY.  Available wherever the head dim is (128 / 256 / 512 in
- * encode, append, forward_qk, forward_ov and decode_attn), except with state checkpoints: ADKV_E_FLAGS. */
+ * error.  Takes precedence over ADKV_FLAG_FAST_REPLAY.  Available in every entry point that takes flags, for the
+ * head dims that entry point serves. */
 #define ADKV_FLAG_HALF_STATE 2u
 
 /* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each
@@ -111,17 +111,18 @@ int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void
                    int B, int H, int T, int D, int n_super_cap, int bits,
                    float scale_min, float scale_max, void *stream);
 
-/* adkv_encode_kv / adkv_append_kv with a `flags` argument (ADKV_FLAG_HALF_STATE selects the arithmetic of the
- * reference's CUDA kernels; 0 is the same as the calls above).  v_cache == NULL: one tensor only (the K
- * arguments).  The tail keeps its float [B, H, 2, D] format in both arithmetics (fp16 state values are stored
- * exactly). */
-int adkv_encode_kv_flags(void *k_cache, const void *k, const adkv_params *kp, void *k_tail,
-                         void *v_cache, const void *v, const adkv_params *vp, void *v_tail,
-                         int B, int H, int T, int D, int n_super_cap, int bits, int t_start,
-                         float scale_min, float scale_max, unsigned flags, void *stream);
-int adkv_append_kv_flags(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail,
-                         void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail,
-                         int B, int H, int T, int D, int n_super_cap, int bits,
+/* The general forms of prefill and append: adkv_encode_kv(_ckpt) / adkv_append_kv(_ckpt) with a `flags` argument
+ * (ADKV_FLAG_HALF_STATE selects the arithmetic of the reference's CUDA kernels; with 0 they are the calls above and
+ * below).  v_cache == NULL: one tensor only (the K arguments; no checkpoints then).  interval == 0: no state
+ * checkpoints (k_ckpt / v_ckpt ignored); otherwise as adkv_encode_kv_ckpt / adkv_append_kv_ckpt.  Tail and
+ * checkpoints keep their float formats in both arithmetics (fp16 state values are stored exactly). */
+int adkv_encode_kv_flags(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                         void *v_cache, const void *v, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                         int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
+                         int t_start, float scale_min, float scale_max, unsigned flags, void *stream);
+int adkv_append_kv_flags(void *k_cache, const void *k_new, const adkv_params *kp, void *k_tail, void *k_ckpt,
+                         void *v_cache, const void *v_new, const adkv_params *vp, void *v_tail, void *v_ckpt,
+                         int interval, int n_ckpt_cap, int B, int H, int T, int D, int n_super_cap, int bits,
                          float scale_min, float scale_max, unsigned flags, void *stream);
 
 /* q.K^T over the packed cache + append of k_new as token T + self logit.  Replaces forward_qk

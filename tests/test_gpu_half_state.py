@@ -218,14 +218,69 @@ def test_varlen_equals_per_sequence_calls():
     assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
 
 
-def test_unsupported_combinations_are_refused():
-    B, H, T = 1, 2, 64
-    k, v, kp, vp, kc, vc = _prefilled(1300, B, H, T, 4)
-    q = synth.gen_q(1301, B, H, D).cuda()
-    ck = gemv.alloc_ckpt(B, H, D, T + 1, 32, "cuda")
-    with pytest.raises(RuntimeError):
-        gemv.decode_attn(q, kc, vc, k[:, :, T:].contiguous(), v[:, :, T:].contiguous(), kp, vp, T, D ** -0.5, SMIN, SMAX,
-                         half_state=True, k_ckpt=ck, v_ckpt=ck.clone(), ckpt_interval=32)
+@pytest.mark.parametrize("bits,Hq,Hkv,T,interval", [(4, 4, 4, 200, 64), (4, 8, 2, 191, 32), (2, 4, 2, 300, 96), (4, 2, 2, 63, 64)])
+def test_checkpointed_decode_equals_plain_decode(bits, Hq, Hkv, T, interval):
+    """State checkpoints in the fp16-state arithmetic: the checkpoints the prefill writes are the states of the numpy
+    restatement at those tokens, and the segment-parallel decode appends the same codes as the plain one."""
+    B = 2
+    k = synth.gen_kv(1700 + T, B, Hkv, T + 1, D, outlier_mode="persistent").cuda()
+    v = synth.gen_kv(1701 + T, B, Hkv, T + 1, D, outlier_mode="persistent").cuda()
+    q = synth.gen_q(1702 + T, B, Hq, D).cuda()
+    kp, vp = live_params(T, Hkv, bits), live_params(T + 1, Hkv, bits)
+    kc, vc = zeros_cache(B, Hkv, T + 1, bits, 1), zeros_cache(B, Hkv, T + 1, bits, 1)
+    kck, vck = gemv.alloc_ckpt(B, Hkv, D, T + 1, interval, "cuda"), gemv.alloc_ckpt(B, Hkv, D, T + 1, interval, "cuda")
+    gemv.encode_kv_pair(kc, k[:, :, :T].contiguous(), kp, vc, v[:, :, :T].contiguous(), vp, SMIN, SMAX, bits=bits,
+                        half_state=True, k_ckpt=kck, v_ckpt=vck, ckpt_interval=interval)
+    # checkpoint j = state before token (j+1)*interval, from the numpy restatement
+    zp0, s0, alpha, beta, target = np16(kp)
+    st = orh.init_state(B, zp0, s0)
+    xs = k[:, :, :T].cpu().numpy()
+    for j in range(T // interval):
+        orh.encode_scan(xs[:, :, j * interval:(j + 1) * interval], st, alpha, beta, target, bits)
+        got = kck[:, :, j].cpu().numpy()
+        assert np.array_equal(got[:, :, 0], st.zp.astype(np.float32)) and np.array_equal(got[:, :, 1], st.sc.astype(np.float32))
+    pk, pv = kc.clone(), vc.clone()
+    kn, vn = k[:, :, T:].contiguous(), v[:, :, T:].contiguous()
+    mask = torch.zeros(B, T + 1, device="cuda")
+    mask[1, : T // 2] = -1e4
+    plain = gemv.decode_attn(q, pk, pv, kn, vn, kp, vp, T, D ** -0.5, SMIN, SMAX, bits=bits, half_state=True, mask=mask)
+    split = gemv.decode_attn(q, kc, vc, kn, vn, kp, vp, T, D ** -0.5, SMIN, SMAX, bits=bits, half_state=True, mask=mask,
+                             k_ckpt=kck, v_ckpt=vck, ckpt_interval=interval)
+    assert torch.equal(kc, pk) and torch.equal(vc, pv)
+    a, b = plain.float(), split.float()
+    torch.testing.assert_close(b, a, rtol=2e-2, atol=2e-2 * max(1.0, float(a.abs().max())))
+    assert gemv.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_appends_keep_the_checkpoints_that_prefill_would_write(bits):
+    B, H, T0, steps, interval = 2, 2, 40, 100, 32
+    x = synth.gen_kv(1800, B, H, T0 + steps, D).cuda()
+    kp, vp = live_params(31, H, bits), live_params(32, H, bits)
+    cap = T0 + steps
+    ck_full, cv_full = gemv.alloc_ckpt(B, H, D, cap, interval, "cuda"), gemv.alloc_ckpt(B, H, D, cap, interval, "cuda")
+    fk, fv = zeros_cache(B, H, cap, bits), zeros_cache(B, H, cap, bits)
+    gemv.encode_kv_pair(fk, x, kp, fv, x, vp, SMIN, SMAX, bits=bits, half_state=True, k_ckpt=ck_full, v_ckpt=cv_full,
+                        ckpt_interval=interval)
+    ck, cv = torch.zeros_like(ck_full), torch.zeros_like(cv_full)
+    pk, pv = torch.zeros_like(fk), torch.zeros_like(fv)
+    tk, tv = (torch.empty(B, H, 2, D, dtype=torch.float32, device="cuda") for _ in range(2))
+    gemv.encode_kv_pair(pk, x[:, :, :T0].contiguous(), kp, pv, x[:, :, :T0].contiguous(), vp, SMIN, SMAX, bits=bits,
+                        half_state=True, k_tail=tk, v_tail=tv, k_ckpt=ck, v_ckpt=cv, ckpt_interval=interval)
+    q = synth.gen_q(1801, B, H, D).cuda()
+    for t in range(T0, T0 + steps):
+        xn = x[:, :, t:t + 1].contiguous()
+        if t % 3 == 0:    # a decode step maintains the checkpoints too (the tail state is not its business)
+            gemv.decode_attn(q, pk, pv, xn, xn, kp, vp, t, D ** -0.5, SMIN, SMAX, bits=bits, half_state=True,
+                             k_ckpt=ck, v_ckpt=cv, ckpt_interval=interval)
+            sk, sv = pk.clone(), pv.clone()       # and the append kernel writes the same code and advances the tails
+            gemv.append_kv_pair(sk, xn, kp, tk, sv, xn, vp, tv, t, SMIN, SMAX, bits=bits, half_state=True)
+            assert torch.equal(sk, pk) and torch.equal(sv, pv)
+        else:
+            gemv.append_kv_pair(pk, xn, kp, tk, pv, xn, vp, tv, t, SMIN, SMAX, bits=bits, half_state=True,
+                                k_ckpt=ck, v_ckpt=cv, ckpt_interval=interval)
+    assert torch.equal(pk, fk) and torch.equal(pv, fv)
+    assert torch.equal(ck, ck_full) and torch.equal(cv, cv_full)
 
 
 @needs_ref

@@ -73,17 +73,20 @@ def test_argument_errors_of_the_flagged_entry_points():
     P = _lib.Params(16, 16, 16, 16, 16)
     pp = ctypes.addressof(P)
     for flags in (0, _lib.FLAG_HALF_STATE):
-        enc = lambda *a: lib.adkv_encode_kv_flags(*a, 0.1, 1.0, flags, None)
+        def enc(kc, k, kpp, kt, vc, v, vpp, vt, *dims, kck=None, vck=None, iv=0, cap=0):
+            return lib.adkv_encode_kv_flags(kc, k, kpp, kt, kck, vc, v, vpp, vt, vck, iv, cap, *dims, 0.1, 1.0, flags, None)
         assert enc(None, 16, pp, None, None, None, None, None, 1, 1, 8, 128, 1, 4, 0) == -1
         assert enc(16, 16, pp, None, None, None, None, None, 1, 1, 8, 64, 1, 4, 0) == -2
         assert enc(16, 16, pp, None, None, None, None, None, 1, 1, 8, 128, 1, 3, 0) == -3
         assert enc(16, 16, pp, None, None, None, None, None, 1, 1, 9, 128, 1, 4, 0) == -5
         assert enc(16, 16, pp, None, None, None, None, None, 1, 1, 4, 128, 1, 4, 4) == -7      # t_start without tail
         assert enc(16, 16, pp, None, 16, None, pp, None, 1, 1, 8, 128, 1, 4, 0) == -1          # V tensor without data
-        app = lambda *a: lib.adkv_append_kv_flags(*a, 0.1, 1.0, flags, None)
+        assert enc(16, 16, pp, None, None, None, None, None, 1, 1, 8, 128, 1, 4, 0, iv=32) == -4   # checkpoints: K and V
+        assert enc(16, 16, pp, None, 16, 16, pp, None, 1, 1, 8, 128, 1, 4, 0, iv=48, kck=16, vck=16, cap=4) == -4
+        assert enc(16, 16, pp, None, 16, 16, pp, None, 1, 1, 8, 128, 1, 4, 0, iv=32, cap=4) == -1  # no checkpoint tensors
+
+        def app(kc, k, kpp, kt, vc, v, vpp, vt, *dims):
+            return lib.adkv_append_kv_flags(kc, k, kpp, kt, None, vc, v, vpp, vt, None, 0, 0, *dims, 0.1, 1.0, flags, None)
         assert app(16, 16, pp, None, None, None, None, None, 1, 1, 3, 128, 1, 4) == -1         # no tail state
         assert app(16, 16, pp, 16, None, None, None, None, 1, 1, 8, 128, 1, 4) == -5
-    # checkpointed decode has no fp16-state form
     assert _lib.strerror(-10).startswith("adkv:")
-    assert lib.adkv_decode_attn_ckpt(16, 16, 16, 16, 16, pp, pp, 16, 16, 32, 4, None, 0, 16, 16, 1 << 20,
-                                     1, 2, 2, 8, 128, 4, 4, 0.1, 0.1, 1.0, _lib.FLAG_HALF_STATE, None) == -10
