@@ -64,3 +64,29 @@ def test_sharding_plan_partitions_the_grid(B, Hkv, world):
         assert s.b1 > s.b0 and s.h1 > s.h0
         seen[s.b0:s.b1, s.h0:s.h1] += 1
     assert (seen == 1).all()
+
+
+@settings(max_examples=15, deadline=None)
+@given(bits=st.sampled_from([2, 4]), T=st.integers(1, 40), cut=st.integers(0, 40), seed=st.integers(0, 2**16))
+def test_fp16_state_restatement_replays_and_chunks_like_the_fp32_one(bits, T, cut, seed):
+    """The numpy restatement of the reference CUDA kernels' arithmetic: the decoder rebuilds the encoder's values and
+    state from the codes, and encoding in two chunks with the state carried over equals encoding in one."""
+    from oracle import adkv_oracle_half as orh
+    rng = np.random.default_rng(seed)
+    H, D = 1, 128
+    x = (rng.standard_normal((1, H, T, D)) * rng.choice([0.1, 1.0, 30.0])).astype(np.float16)
+    p = (rng.standard_normal((H, D)).astype(np.float16), (rng.random((H, D)) * 2 + 0.01).astype(np.float16),
+         (rng.random((H, D)) * 0.3).astype(np.float16), (rng.random((H, D)) * 0.1).astype(np.float16),
+         (rng.random((H, D)) * 4).astype(np.float16))
+    st_enc = orh.init_state(1, p[0], p[1])
+    codes, xhat = orh.encode_scan(x, st_enc, p[2], p[3], p[4], bits)
+    st_dec = orh.init_state(1, p[0], p[1])
+    xhat2 = orh.decode_scan(codes, st_dec, p[2], p[3], p[4])
+    same = lambda a, b: np.array_equal(a.view(np.uint16), b.view(np.uint16))
+    assert same(xhat, xhat2) and same(st_enc.zp, st_dec.zp) and same(st_enc.sc, st_dec.sc)
+    c = min(cut, T)
+    st2 = orh.init_state(1, p[0], p[1])
+    c1, _ = orh.encode_scan(x[:, :, :c], st2, p[2], p[3], p[4], bits)
+    c2, _ = orh.encode_scan(x[:, :, c:], st2, p[2], p[3], p[4], bits)
+    assert np.array_equal(np.concatenate([c1, c2], axis=2), codes)
+    assert same(st2.zp, st_enc.zp) and same(st2.sc, st_enc.sc)
