@@ -10,7 +10,8 @@ import pytest
 from adkv_b200 import gemv, hf_shim
 
 # a checkout of the reference project, when one is available (the comparison is skipped otherwise)
-REF = os.environ.get("ADKV_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+REF = os.environ.get("ADKV_REFERENCE_ROOT",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.pardir, "reference"))
 
 
 def test_install_registers_module_under_reference_name():
