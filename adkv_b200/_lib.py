@@ -15,10 +15,13 @@ c_void_p, c_int, c_float, c_uint, c_longlong = (ctypes.c_void_p, ctypes.c_int, c
 
 FLAG_FAST_REPLAY = 1
 FLAG_HALF_STATE = 2
+FLAG_TAIL_KEEP = 4
+ABI_VERSION = 2
 
 
-def flags(fast: bool = False, half_state: bool = False) -> int:
-    return (FLAG_FAST_REPLAY if fast else 0) | (FLAG_HALF_STATE if half_state else 0)
+def flags(fast: bool = False, half_state: bool = False, tail_keep: bool = False) -> int:
+    return (FLAG_FAST_REPLAY if fast else 0) | (FLAG_HALF_STATE if half_state else 0) | \
+        (FLAG_TAIL_KEEP if tail_keep else 0)
 
 # name -> argument types (return type is int unless listed in _RESTYPE); mirrors include/adkv_b200.h
 SIGNATURES = {
@@ -35,10 +38,10 @@ SIGNATURES = {
     "adkv_encode_kv_ckpt": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_void_p],
     "adkv_append_kv_ckpt": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_void_p],
     "adkv_decode_attn_ckpt_scratch_bytes": [c_int, c_int, c_int, c_int, c_int],
-    "adkv_decode_attn_ckpt": [c_void_p] * 9 + [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+    "adkv_decode_attn_ckpt": [c_void_p] * 11 + [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_uint,
                               c_void_p],
-    "adkv_decode_attn_ckpt_static": [c_void_p] * 9 + [c_int, c_int, c_void_p, c_longlong, c_void_p,
+    "adkv_decode_attn_ckpt_static": [c_void_p] * 11 + [c_int, c_int, c_void_p, c_longlong, c_void_p,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float,
                                      c_uint, c_void_p],
     "adkv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -47,10 +50,9 @@ SIGNATURES = {
                         c_int, c_int, c_float, c_float, c_uint, c_void_p],
     "adkv_forward_ov": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                         c_int, c_int, c_float, c_float, c_uint, c_void_p],
-    "adkv_decode_attn": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "adkv_decode_attn": [c_void_p] * 10 + [c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_float, c_float, c_float, c_uint, c_void_p],
-    "adkv_decode_attn_varlen": [c_void_p] * 9 + [c_int] * 6 + [c_float, c_float, c_float, c_uint, c_void_p],
+    "adkv_decode_attn_varlen": [c_void_p] * 11 + [c_int] * 6 + [c_float, c_float, c_float, c_uint, c_void_p],
     "adkv_device_status": [c_void_p, c_void_p],
     "adkv_selftest_wait_timeout": [c_int, c_void_p],
 }
@@ -85,7 +87,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _RESTYPE.get(name, c_int)
-    if lib.adkv_abi_version() != 1:
+    if lib.adkv_abi_version() != ABI_VERSION:
         raise RuntimeError("libadkv_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -44,7 +44,9 @@ const char *adkv_strerror(int code)
     case ADKV_E_ALIGN: return "adkv: pointer not sufficiently aligned (cache 16 bytes, fp16 rows 8 bytes)";
     case ADKV_E_START: return "adkv: t_start > 0 needs a tail state";
     case ADKV_E_SCRATCH: return "adkv: scratch memory too small for this problem";
-    case ADKV_E_FLAGS: return "adkv: a flag is not available for this entry point";
+    case ADKV_E_FLAGS:
+        return "adkv: flag or optional argument not available in this combination (tail states need both tensors and "
+               "the fp32 arithmetic)";
     case ADKV_E_STATIC_MAX:
         return "adkv: problem needs more than the 16 MiB of built-in scratch (ADKV_STATIC_SCRATCH_BYTES); use "
                "adkv_decode_attn_ckpt with caller-owned scratch, or a larger checkpoint interval";

@@ -21,6 +21,14 @@ constexpr int kTileTok = 32;   // tokens per tile
 constexpr int kStages = 3;     // bulk-copy ring depth per warp
 constexpr int kLogitSlots = 4; // logits ring depth (fused kernel)
 
+// Replay arithmetic of the fp32 recurrence (template parameter ARITH of the scans below):
+//   kArithFma   contracted: zp = fma(alpha, q*s, zp), s = s * fma(beta, |q|, 1 - beta*target)
+//   kArithCanon the reference's order, one rounding per operation (src/adkv/train/train_model.py:70-81)
+// (2 is taken by the fp16-state arithmetic, adkv_half.cuh.)  Only kArithCanon reproduces the encoder's state bit
+// for bit.  kArithFma is meant for decoding next to a persisted tail state (KArgs::tail), which then supplies
+// the canonical state the appended token is quantised with.
+constexpr int kArithFma = 0, kArithCanon = 1;
+
 template <int BITS>
 struct Tile {
     static constexpr int WORDS = kTileTok / Codec<BITS>::TPW;   // words per channel per tile
@@ -221,7 +229,53 @@ struct KArgs {
     int Hq, Hkv, T, n_super_cap;
     float smin, smax;
     int D;                  // head dim (128, 256 or 512)
+    float *tail = nullptr;  // [B, Hkv, 2, D] canonical state after token T-1 (zp then scale), or nullptr
+    bool tail_keep = false; // leave `tail` as it is instead of advancing it over the appended token
 };
+
+// Append the new token of this lane's 4 channels as token T: quantise, merge the code into word `slot`, return the
+// dequantised values in xh.  Without a tail the state the replay left in `ch` is used (it is the encoder's state
+// only when the replay was canonical).  With a tail the token is quantised with that state -- the canonical one
+// after token T-1, as encode / append / an earlier decode step left it -- whatever arithmetic replayed the cache,
+// and the tail then advances canonically; `ch` is not read.  ckpt_out, if set, receives the state after token T.
+template <int BITS, int ARITH>
+__device__ __forceinline__ void append_new_token(Chan (&ch)[4], const ParamPtrs &p, size_t poff, float *tail,
+                                                 bool tail_keep, const __half *x_new, uint4 *slot, int T, float smin,
+                                                 float smax, float *ckpt_out, int c0, int D, float (&xh)[4])
+{
+    using C = Codec<BITS>;
+    float xn[4];
+    load_half4(xn, x_new);
+    uint4 wv = *slot;
+    uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    const int sh = BITS * (T % C::TPW);
+    if (tail) {
+        float tg[4];
+        load_half4(tg, p.target + poff);
+        load_init_state(ch, tail, c0, D);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            ch[c].tc = tg[c];   // canonical form of the constant, whatever the replay used
+            float rh;
+            const float q = quantize<BITS>(xn[c], ch[c], rh);
+            xh[c] = __fadd_rn(rh, ch[c].zp);
+            ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+            advance_canonical(q, rh, ch[c], smin, smax);
+        }
+        if (!tail_keep) store_state(tail, ch, c0, D);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float rh;
+            const float q = quantize<BITS>(xn[c], ch[c], rh);
+            xh[c] = __fadd_rn(rh, ch[c].zp);
+            ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
+            if (ckpt_out) advance_like_replay<ARITH == kArithCanon>(q, rh, ch[c], smin, smax);
+        }
+    }
+    *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+    if (ckpt_out) store_state(ckpt_out, ch, c0, D);
+}
 
 // Sink interface (duck-typed):
 //   bool begin_tile(int i)            wait for room; false = bounded wait gave up
@@ -229,11 +283,12 @@ struct KArgs {
 //   void end_tile(int i, int lane)
 //   void put_self(int g, float v)     lane 0
 //   void finish(int lane)
-template <int BITS, int G, bool EXACT, class Sink, int STAGES = kStages, bool WIDE = false>
+template <int BITS, int G, int ARITH, class Sink, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, float *red, Sink &sink)
 {
     using C = Codec<BITS>;
+    constexpr bool EXACT = ARITH == kArithCanon;
     const int bh = b * a.Hkv + h;
     const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
     const int c0 = kD * slice + 4 * lane;      // first of this lane's 4 channels within the head
@@ -313,24 +368,13 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
     }
 
     if (!seg.append) return;
-    // Append k_new as token T with the state left by token T-1, then its own logit from the
+    // Append k_new as token T with the state after token T-1, then its own logit from the
     // dequantised value.
-    float xn[4], xh[4];
-    load_half4(xn, a.x_new + size_t(bh) * D + c0);
-    uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
-    uint4 wv = *slot;
-    uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-    const int sh = BITS * (a.T % C::TPW);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        float rh;
-        const float q = quantize<BITS>(xn[c], ch[c], rh);
-        xh[c] = __fadd_rn(rh, ch[c].zp);
-        ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
-        if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
-    }
-    *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
-    if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, D);
+    float xh[4];
+    append_new_token<BITS, ARITH>(ch, a.p, size_t(h) * D + c0, a.tail ? a.tail + size_t(bh) * 2 * D : nullptr,
+                                  a.tail_keep, a.x_new + size_t(bh) * D + c0,
+                                  reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane, a.T,
+                                  a.smin, a.smax, seg.ckpt_out, c0, D, xh);
     if (!sink.begin_tile(ring.n_tiles)) return;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -434,7 +478,16 @@ struct VArgs {
     int Hq, Hkv, T, n_super_cap;
     float smin, smax;
     int D;                  // head dim (128, 256 or 512)
+    float *tail = nullptr;  // as KArgs::tail, for the V cache
+    bool tail_keep = false;
 };
+
+// A V scan that gives up on a bounded wait tells its source, if the source cares (give_up is optional): the
+// checkpointed kernel's source then marks its partial result as unusable instead of leaving stale memory behind.
+template <class S>
+__device__ __forceinline__ auto src_give_up(S &s, int c0, int) -> decltype(s.give_up(c0), void()) { s.give_up(c0); }
+template <class S>
+__device__ __forceinline__ void src_give_up(S &, int, long) {}
 
 // Source interface (duck-typed):
 //   bool tile_weights(int i, int ntok, int lane, float (&acc)[G][4])
@@ -442,11 +495,13 @@ struct VArgs {
 //        false = bounded wait gave up
 //   bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
 //   void store(const VArgs&, int b, int h, int c0, const float (&acc)[G][4])   write the result (c0: first channel)
-template <int BITS, int G, bool EXACT, class Src, int STAGES = kStages, bool WIDE = false>
+//   void give_up(int c0)              optional: called instead of store() when a bounded wait gave up
+template <int BITS, int G, int ARITH, class Src, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, const float2 *wts, Src &src)
 {
     using C = Codec<BITS>;
+    constexpr bool EXACT = ARITH == kArithCanon;
     const int bh = b * a.Hkv + h;
     const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
     const int c0 = kD * slice + 4 * lane;
@@ -510,28 +565,21 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
     }
     if (!ok) {
         ring.drain(i);
+        src_give_up(src, c0, 0);
         return;
     }
 
     if (seg.append) {
         float w_self[G];
-        if (!src.self_weight(lane, acc, w_self, a.T)) return;
-        float xn[4], xh[4];
-        load_half4(xn, a.x_new + size_t(bh) * D + c0);
-        uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
-        uint4 wv = *slot;
-        uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-        const int sh = BITS * (a.T % C::TPW);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float rh;
-            const float q = quantize<BITS>(xn[c], ch[c], rh);
-            xh[c] = __fadd_rn(rh, ch[c].zp);
-            ww[c] = (ww[c] & ~(C::FIELD << sh)) | (uint32_t(int(q) + C::BIAS) << sh);
-            if (seg.ckpt_out) advance_like_replay<EXACT>(q, rh, ch[c], a.smin, a.smax);
+        if (!src.self_weight(lane, acc, w_self, a.T)) {
+            src_give_up(src, c0, 0);
+            return;
         }
-        *slot = make_uint4(ww[0], ww[1], ww[2], ww[3]);
-        if (seg.ckpt_out) store_state(seg.ckpt_out, ch, c0, D);
+        float xh[4];
+        append_new_token<BITS, ARITH>(ch, a.p, size_t(h) * D + c0, a.tail ? a.tail + size_t(bh) * 2 * D : nullptr,
+                                      a.tail_keep, a.x_new + size_t(bh) * D + c0,
+                                      reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane, a.T,
+                                      a.smin, a.smax, seg.ckpt_out, c0, D, xh);
 #pragma unroll
         for (int g = 0; g < G; ++g)
 #pragma unroll

@@ -9,7 +9,7 @@ namespace adkv {
 // =========================================================================================
 // Fused decode step: one CTA per (batch, kv head); warp 0 scans K, warp 1 scans V.
 
-template <int BITS, int G, bool EXACT>
+template <int BITS, int G, int ARITH>
 __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
                                                          long long mask_stride_b, float scaling,
                                                          const int *__restrict__ seq_lens)
@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
     const Seg seg{0, ka.T, true, nullptr, nullptr, 0};
     if (warp == 0) {
         RingSink<G> sink{&fs, 0, 0};
-        k_warp<BITS, G, EXACT>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
+        k_warp<BITS, G, ARITH>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         SoftmaxSrc<G> src;
         src.sh = &fs;
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
         src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
         src.t_begin = 0;
         src.init();
-        v_warp<BITS, G, EXACT>(va, seg, b, h, lane, vbuf, vbar, wts, src);
+        v_warp<BITS, G, ARITH>(va, seg, b, h, lane, vbuf, vbar, wts, src);
     }
 }
 
@@ -71,21 +71,25 @@ ADKV_DEFINE_TU_STATUS(adkv_tu_status_fused)
 extern "C" {
 
 int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                     const adkv_params *kp, const adkv_params *vp, const void *mask, long long mask_stride_b,
+                     const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail, const void *mask,
+                     long long mask_stride_b,
                      void *out, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scaling,
                      float scale_min, float scale_max, unsigned flags, void *stream)
 {
     if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !params_ok(kp) || !params_ok(vp))
         return ADKV_E_NULL;
     if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (int rc = check_tails(k_tail, v_tail, flags)) return rc;
     if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
         !aligned8(v_new) || !params_aligned(kp) || !params_aligned(vp))
         return ADKV_E_ALIGN;
     if (B == 0) return 0;
+    const bool keep = flags & ADKV_FLAG_TAIL_KEEP;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D,
+                   static_cast<float *>(k_tail), keep};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
+                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D, static_cast<float *>(v_tail), keep};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool half = flags & ADKV_FLAG_HALF_STATE, exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     if (D != kD)
@@ -94,34 +98,37 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
     if (half)
         return adkv_half_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, nullptr, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
-                  (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(
+                  (decode_attn_kernel<BITS, G, ARITH><<<B * Hkv, 64, 0, s>>>(
                       ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, nullptr)))
     return launch_status();
 }
 
 int adkv_decode_attn_varlen(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                            const adkv_params *kp, const adkv_params *vp, const void *seq_lens, void *out, int B,
-                            int Hq, int Hkv, int D, int n_super_cap, int bits, float scaling, float scale_min,
-                            float scale_max, unsigned flags, void *stream)
+                            const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail,
+                            const void *seq_lens, void *out, int B, int Hq, int Hkv, int D, int n_super_cap, int bits,
+                            float scaling, float scale_min, float scale_max, unsigned flags, void *stream)
 {
     if (!q || !k_cache || !v_cache || !k_new || !v_new || !out || !seq_lens || !params_ok(kp) || !params_ok(vp))
         return ADKV_E_NULL;
     if (D != kD) return ADKV_E_HEAD_DIM;   // device-side lengths: 128-wide heads only
     if (int rc = check_common(B, Hq, Hkv, 0, D, n_super_cap, bits, 1)) return rc;
+    if (int rc = check_tails(k_tail, v_tail, flags)) return rc;
     if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
         !aligned8(v_new) || !params_aligned(kp) || !params_aligned(vp) || (reinterpret_cast<uintptr_t>(seq_lens) & 3u))
         return ADKV_E_ALIGN;
     if (B == 0) return 0;
+    const bool keep = flags & ADKV_FLAG_TAIL_KEEP;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D};
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D,
+                   static_cast<float *>(k_tail), keep};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(vp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D};
+                   to_ptrs(vp), Hq, Hkv, 0, n_super_cap, scale_min, scale_max, D, static_cast<float *>(v_tail), keep};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (flags & ADKV_FLAG_HALF_STATE)
         return adkv_half_decode_attn(ka, va, nullptr, 0, scaling, B, bits, static_cast<const int *>(seq_lens), s);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
-                  (decode_attn_kernel<BITS, G, EXACT><<<B * Hkv, 64, 0, s>>>(ka, va, nullptr, 0, scaling,
+                  (decode_attn_kernel<BITS, G, ARITH><<<B * Hkv, 64, 0, s>>>(ka, va, nullptr, 0, scaling,
                                                                             static_cast<const int *>(seq_lens))))
     return launch_status();
 }

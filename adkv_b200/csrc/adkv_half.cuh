@@ -430,12 +430,16 @@ __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, 
     }
     if (!ok) {
         ring.drain(i);
+        src_give_up(src, c0, 0);
         return;
     }
 
     if (seg.append) {   // gemv.cu:1105-1159
         float w_self[G];
-        if (!src.self_weight(lane, acc, w_self, a.T)) return;
+        if (!src.self_weight(lane, acc, w_self, a.T)) {
+            src_give_up(src, c0, 0);
+            return;
+        }
         const uint2 xn = *reinterpret_cast<const uint2 *>(a.x_new + size_t(bh) * D + c0);
         const h2 xnp[2] = {xn.x, xn.y};
         uint4 *slot = reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane;
@@ -463,8 +467,8 @@ __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, 
     src.store(a, b, h, c0, acc);
 }
 
-// Scan of one tensor of a stream in the arithmetic MODE selects: 0 = fp32 recurrence, contracted replay;
-// 1 = fp32 recurrence, canonical order; 2 = the fp16-state arithmetic above.
+// Scan of one tensor of a stream in the arithmetic MODE selects: kArithFma (0) and kArithCanon (1) are the fp32
+// recurrence (adkv_decode.cuh); 2 = the fp16-state arithmetic above.
 constexpr int kModeHalf = 2;
 
 template <int BITS, int G, int MODE, class Sink, int ST = kStages, bool WIDE = false>
@@ -472,7 +476,7 @@ __device__ __forceinline__ void k_scan(const KArgs &a, const Seg &seg, int b, in
                                        float *red, Sink &sink)
 {
     if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
-    else k_warp<BITS, G, MODE == 1, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
+    else k_warp<BITS, G, MODE, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
 }
 
 template <int BITS, int G, int MODE, class Src, int ST = kStages, bool WIDE = false>
@@ -480,7 +484,7 @@ __device__ __forceinline__ void v_scan(const VArgs &a, const Seg &seg, int b, in
                                        const float2 *wts, Src &src)
 {
     if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
-    else v_warp<BITS, G, MODE == 1, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
+    else v_warp<BITS, G, MODE, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
 }
 
 }  // namespace adkv

@@ -44,6 +44,15 @@ static inline int check_common(int B, int Hq, int Hkv, int T, int D, int n_super
     return 0;
 }
 
+// Tail states of the decode entry points: both or neither, 16-byte aligned, fp32 arithmetic only.
+static inline int check_tails(const void *k_tail, const void *v_tail, unsigned flags)
+{
+    if (!k_tail && !v_tail) return 0;
+    if (!k_tail || !v_tail || (flags & ADKV_FLAG_HALF_STATE)) return ADKV_E_FLAGS;
+    if (!aligned16(k_tail) || !aligned16(v_tail)) return ADKV_E_ALIGN;
+    return 0;
+}
+
 // Every translation unit that includes adkv_device.cuh has its own device status word; this defines the hidden
 // function through which adkv_device_status reads and clears the one of the unit it is expanded in.
 #define ADKV_DEFINE_TU_STATUS(fn_name)                                                \
@@ -56,13 +65,13 @@ static inline int check_common(int B, int Hq, int Hkv, int T, int D, int n_super
         return e == cudaSuccess ? 0 : int(e);                                         \
     }
 
-// Dispatch over (bits, group size, arithmetic).
+// Dispatch over (bits, group size, arithmetic).  CALL sees BITS, G, EXACT and ARITH (kArithCanon / kArithFma).
 #define ADKV_DISPATCH_G(BITS_, EXACT_, G_, CALL) \
     switch (G_) {                                \
-    case 1: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 1; CALL; } break; \
-    case 2: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 2; CALL; } break; \
-    case 4: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 4; CALL; } break; \
-    case 8: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int G = 8; CALL; } break; \
+    case 1: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int ARITH = EXACT_ ? 1 : 0; constexpr int G = 1; (void)EXACT; (void)ARITH; CALL; } break; \
+    case 2: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int ARITH = EXACT_ ? 1 : 0; constexpr int G = 2; (void)EXACT; (void)ARITH; CALL; } break; \
+    case 4: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int ARITH = EXACT_ ? 1 : 0; constexpr int G = 4; (void)EXACT; (void)ARITH; CALL; } break; \
+    case 8: { constexpr int BITS = BITS_; constexpr bool EXACT = EXACT_; constexpr int ARITH = EXACT_ ? 1 : 0; constexpr int G = 8; (void)EXACT; (void)ARITH; CALL; } break; \
     default: return ADKV_E_SHAPE;                \
     }
 #define ADKV_DISPATCH(bits_, exact_, G_, CALL)                            \

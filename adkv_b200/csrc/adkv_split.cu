@@ -32,6 +32,20 @@ struct PartialSrc : SoftmaxSrc<G, 1, HALF_W> {
                 make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
         }
     }
+    // The segment could not be finished (a bounded wait gave up; the status word says which): leave a partial
+    // that turns the merged output of these heads into NaN, so that neither the scratch contents of an earlier
+    // call nor an output that silently lacks a segment can pass for a result.
+    __device__ __forceinline__ void give_up(int c0) const
+    {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (c0 == 0) {
+                part[g * kPartStride] = -INFINITY;
+                part[g * kPartStride + 1] = __int_as_float(0x7fc00000);
+            }
+            *reinterpret_cast<float4 *>(part + g * kPartStride + 4 + c0) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
 };
 
 struct CkptArgs {
@@ -148,8 +162,8 @@ long long adkv_decode_attn_ckpt_scratch_bytes(int B, int Hq, int Hkv, int T, int
 }
 
 int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                          const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt, int interval,
-                          int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out, void *scratch,
+                          const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail, void *k_ckpt,
+                          void *v_ckpt, int interval, int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out, void *scratch,
                           long long scratch_bytes, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
                           float scaling, float scale_min, float scale_max, unsigned flags, void *stream)
 {
@@ -158,6 +172,7 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
         return ADKV_E_NULL;
     if (D != kD) return ADKV_E_HEAD_DIM;   // checkpointed decode: 128-wide heads only
     if (int rc = check_common(B, Hq, Hkv, T, D, n_super_cap, bits, T + 1)) return rc;
+    if (int rc = check_tails(k_tail, v_tail, flags)) return rc;
     if (interval <= 0 || interval % kTileTok != 0 || n_ckpt_cap < 0) return ADKV_E_SHAPE;
     if ((T + 1) / interval > n_ckpt_cap) return ADKV_E_CAPACITY;
     if (!aligned16(k_cache) || !aligned16(v_cache) || !aligned8(q) || !aligned8(out) || !aligned8(k_new) ||
@@ -166,10 +181,12 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
         return ADKV_E_ALIGN;
     if (scratch_bytes < adkv_decode_attn_ckpt_scratch_bytes(B, Hq, Hkv, T, interval)) return ADKV_E_SCRATCH;
     if (B == 0) return 0;
+    const bool keep = flags & ADKV_FLAG_TAIL_KEEP;
     const KArgs ka{static_cast<const __half *>(q), static_cast<uint8_t *>(k_cache),
-                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
+                   static_cast<const __half *>(k_new), to_ptrs(kp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D,
+                   static_cast<float *>(k_tail), keep};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
-                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D};
+                   to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D, static_cast<float *>(v_tail), keep};
     const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
@@ -183,7 +200,7 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
                           static_cast<float *>(scratch))))
     } else {
         ADKV_DISPATCH(bits, exact, Hq / Hkv,
-                      (decode_attn_split_kernel<BITS, G, int(EXACT)><<<grid, 64, 0, s>>>(
+                      (decode_attn_split_kernel<BITS, G, ARITH><<<grid, 64, 0, s>>>(
                           ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, ck,
                           static_cast<float *>(scratch))))
     }
@@ -237,8 +254,8 @@ static int static_scratch_of_current_device(float **addr)
 extern "C" {
 
 int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                                 const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt,
-                                 int interval, int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out,
+                                 const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail,
+                                 void *k_ckpt, void *v_ckpt, int interval, int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out,
                                  int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scaling,
                                  float scale_min, float scale_max, unsigned flags, void *stream)
 {
@@ -248,9 +265,10 @@ int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, co
     float *scratch = nullptr;
     if (int rc = static_scratch_of_current_device(&scratch)) return rc;
     // Nothing in the array has to start at zero: the segment kernel writes every slot the merge kernel
-    // reads, so what an earlier call left behind is simply overwritten.
-    return adkv_decode_attn_ckpt(q, k_cache, v_cache, k_new, v_new, kp, vp, k_ckpt, v_ckpt, interval, n_ckpt_cap,
-                                 mask, mask_stride_b, out, scratch, (long long)ADKV_STATIC_SCRATCH_BYTES, B, Hq, Hkv,
+    // reads -- its result, or a NaN marker where a bounded wait gave up -- so what an earlier call left
+    // behind is always overwritten.
+    return adkv_decode_attn_ckpt(q, k_cache, v_cache, k_new, v_new, kp, vp, k_tail, v_tail, k_ckpt, v_ckpt, interval,
+                                 n_ckpt_cap, mask, mask_stride_b, out, scratch, (long long)ADKV_STATIC_SCRATCH_BYTES, B, Hq, Hkv,
                                  T, D, n_super_cap, bits, scaling, scale_min, scale_max, flags, stream);
 }
 

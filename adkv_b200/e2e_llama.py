@@ -7,7 +7,9 @@ prefill runs dense causal attention on the prompt and quantises K/V into the pac
 (``llama_adkv.py:358-378``), every decode step attends over the packed cache and appends the new
 token (``llama_adkv.py:347-355``).  Differences that make it a B200 serving loop rather than a
 port: caches are sized once for prompt + generation; one fused ``decode_attn`` launch per layer
-replaces qk -> softmax -> ov; K and V of a layer are quantised in one launch; and the model can be
+replaces qk -> softmax -> ov; K and V of a layer are quantised in one launch; the recurrence state after the
+last token is kept per layer (tail states), so every appended code comes from it bit-exactly while the replay
+of the cache runs in the cheaper contracted arithmetic; and the model can be
 tensor-parallel over the GPUs of a node (heads and FFN columns sharded, two NCCL all-reduces per
 layer on the ``[B, d_model]`` activations, which are the only NVLink traffic -- attention itself
 never leaves its GPU).
@@ -68,12 +70,19 @@ class ADKVLlama:
     """One tensor-parallel shard of the model with its packed KV caches."""
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, bits: int = 4, device="cuda",
-                 rank: int = 0, world: int = 1, seed: int = 0, fused: bool = True, fast: bool = False,
-                 ckpt_interval: int = 0, half_state: bool = False):
+                 rank: int = 0, world: int = 1, seed: int = 0, fused: bool = True, fast: bool | None = None,
+                 ckpt_interval: int = 0, half_state: bool = False, peers: list | None = None):
+        """``fast``: None = contracted replay wherever tail states keep the stored codes exact (the fused step in the
+        fp32 arithmetic), canonical replay otherwise.  ``peers``: the other tensor-parallel shards when all of them
+        live in this process (tests on one GPU); the all-reduce is then a sum over the shards' partial results, and
+        the shards are stepped together with :func:`step_together`."""
         assert shape.n_heads % world == 0 and shape.n_kv_heads % world == 0 and shape.ffn % world == 0
         self.s, self.B, self.bits, self.dev = shape, batch, bits, torch.device(device)
-        self.rank, self.world, self.fused, self.fast, self.ckpt_interval = rank, world, fused, fast, ckpt_interval
+        self.rank, self.world, self.fused, self.ckpt_interval = rank, world, fused, ckpt_interval
         self.half_state = half_state
+        self.keeps_tails = fused and not half_state
+        self.fast = self.keeps_tails if fast is None else fast
+        self.peers = peers
         self.hq, self.hkv, self.ffn = shape.n_heads // world, shape.n_kv_heads // world, shape.ffn // world
         D, dm = shape.head_dim, shape.d_model
         g = torch.Generator(device=self.dev)
@@ -115,6 +124,9 @@ class ADKVLlama:
         for L in self.layers:
             L["kc"] = torch.zeros((batch, self.hkv, ns, D // 4, 4, 4), dtype=torch.uint8, device=self.dev)
             L["vc"] = torch.zeros_like(L["kc"])
+            if self.keeps_tails:
+                L["kt"] = torch.zeros((batch, self.hkv, 2, D), dtype=torch.float32, device=self.dev)
+                L["vt"] = torch.zeros_like(L["kt"])
             if ckpt_interval:
                 L["kck"] = gemv.alloc_ckpt(batch, self.hkv, D, max_tokens, ckpt_interval, self.dev)
                 L["vck"] = gemv.alloc_ckpt(batch, self.hkv, D, max_tokens, ckpt_interval, self.dev)
@@ -129,8 +141,15 @@ class ADKVLlama:
     # ------------------------------------------------------------------ helpers
     def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
+            if self.peers is not None:      # shards of one process: summed by step_together
+                raise RuntimeError("shards that share a process are stepped with step_together()")
             dist.all_reduce(x)
         return x
+
+    def _tails(self, L, b0=None, b1=None):
+        if not self.keeps_tails:
+            return {}
+        return dict(k_tail=L["kt"][b0:b1], v_tail=L["vt"][b0:b1])
 
     def _mlp(self, L, x):
         gu = x @ L["w_gate_up"].T
@@ -153,7 +172,7 @@ class ADKVLlama:
         B, Tp = ids.shape
         assert B == self.B and self.T == 0
         cos, sin = self.cos[:Tp], self.sin[:Tp]
-        nxt = []
+        logits = []
         for b0 in range(0, B, batch_chunk):
             b1 = min(B, b0 + batch_chunk)
             x = self.embed[ids[b0:b1]]
@@ -163,15 +182,49 @@ class ADKVLlama:
                 q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
                 gemv.encode_kv_pair(L["kc"][b0:b1], k.contiguous(), L["kp"], L["vc"][b0:b1], v.contiguous(), L["vp"],
                                     synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, half_state=self.half_state,
+                                    **self._tails(L, b0, b1),
                                     **({"k_ckpt": L["kck"][b0:b1], "v_ckpt": L["vck"][b0:b1],
                                         "ckpt_interval": self.ckpt_interval} if self.ckpt_interval else {}))
                 att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.hq != self.hkv)
                 x = x + self._allreduce(att.transpose(1, 2).reshape(b1 - b0, Tp, -1) @ L["wo"].T)
                 x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
             last = _rms_norm(x[:, -1], self.final_norm, self.s.norm_eps)
-            nxt.append((last @ self.lm_head.T).argmax(-1))
+            logits.append(last @ self.lm_head.T)
         self.T = Tp
-        return torch.cat(nxt)
+        self.last_logits = torch.cat(logits)
+        return self.last_logits.argmax(-1)
+
+    # ------------------------------------------------------------------ the two halves of a layer, before the all-reduce
+    def _attn_partial(self, L, x, T, cos, sin, seq_lens=None):
+        """This shard's part of the attention block's output for one new token per sequence: [B, 1, d_model]."""
+        h = _rms_norm(x, L["norm1"], self.s.norm_eps)
+        q, k, v = self._qkv(L, h, 1)
+        q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
+        v = v.contiguous()
+        smin, smax = synth.SCALE_MIN, synth.SCALE_MAX
+        if seq_lens is not None:
+            att = gemv.decode_attn_varlen(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], seq_lens, self.scaling, smin, smax,
+                                          bits=self.bits, fast=self.fast, half_state=self.half_state, **self._tails(L))
+        elif self.fused:
+            att = gemv.decode_attn(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], T, self.scaling, smin, smax,
+                                   bits=self.bits, fast=self.fast, half_state=self.half_state, scratch=self.scratch,
+                                   **self._tails(L), **self._ck(L))
+        else:   # the reference caller's three-call sequence (llama_adkv.py:263-276)
+            logits = gemv.forward_qk(q, L["kc"], k, *L["kp"], T, smin, smax, bits=self.bits, fast=self.fast,
+                                     half_state=self.half_state)
+            w = torch.softmax(logits.float() * self.scaling, dim=-1).to(torch.float16)
+            att = gemv.forward_ov(w, L["vc"], v, *L["vp"], smin, smax, bits=self.bits, fast=self.fast,
+                                  half_state=self.half_state)
+        return att.reshape(self.B, 1, -1) @ L["wo"].T
+
+    def _mlp_partial(self, L, x):
+        gu = _rms_norm(x, L["norm2"], self.s.norm_eps) @ L["w_gate_up"].T
+        return (F.silu(gu[..., :self.ffn]) * gu[..., self.ffn:]) @ L["w_down"].T
+
+    def _head(self, x):
+        last = _rms_norm(x[:, 0], self.final_norm, self.s.norm_eps)
+        self.last_logits = last @ self.lm_head.T
+        return self.last_logits.argmax(-1)
 
     # ------------------------------------------------------------------ decode, replayable
     @torch.no_grad()
@@ -183,22 +236,20 @@ class ADKVLlama:
         cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
         x = self.embed[ids][:, None, :]
         for L in self.layers:
-            h = _rms_norm(x, L["norm1"], self.s.norm_eps)
-            q, k, v = self._qkv(L, h, 1)
-            q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
-            att = gemv.decode_attn_varlen(q, L["kc"], L["vc"], k, v.contiguous(), L["kp"], L["vp"], self.seq_lens,
-                                          self.scaling, synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits,
-                                          fast=self.fast, half_state=self.half_state)
-            x = x + self._allreduce(att.reshape(self.B, 1, -1) @ L["wo"].T)
-            x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
+            x = x + self._allreduce(self._attn_partial(L, x, None, cos, sin, seq_lens=self.seq_lens))
+            x = x + self._allreduce(self._mlp_partial(L, x))
         self.seq_lens += 1
-        last = _rms_norm(x[:, 0], self.final_norm, self.s.norm_eps)
-        return (last @ self.lm_head.T).argmax(-1)
+        return self._head(x)
 
     @torch.no_grad()
     def capture_decode(self, warmup_ids: torch.Tensor, warmup_steps: int = 3) -> torch.Tensor:
         """Run `warmup_steps` real decode steps eagerly, then record one step into a CUDA graph.
-        Returns the token ids after the warm-up steps; continue with :meth:`decode_replay`."""
+        Returns the token ids after the warm-up steps; continue with :meth:`decode_replay`.  The recorded step is
+        the fused kernel with device-side lengths: the three-call sequence and checkpointed decode take the token
+        count from the host and are refused here rather than silently replaced."""
+        if not self.fused or self.ckpt_interval:
+            raise ValueError("the replayable decode step is the fused kernel without state checkpoints "
+                             "(fused=True, ckpt_interval=0)")
         self.seq_lens = torch.full((self.B,), self.T, dtype=torch.int32, device=self.dev)
         self._g_in = warmup_ids.clone()
         side = torch.cuda.Stream(device=self.dev)
@@ -230,28 +281,55 @@ class ADKVLlama:
         cos, sin = self.cos[T:T + 1], self.sin[T:T + 1]
         x = self.embed[ids][:, None, :]                                                  # [B, 1, dm]
         for L in self.layers:
-            h = _rms_norm(x, L["norm1"], self.s.norm_eps)
-            q, k, v = self._qkv(L, h, 1)
-            q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
-            v = v.contiguous()
-            if self.fused:
-                att = gemv.decode_attn(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], T, self.scaling,
-                                       synth.SCALE_MIN, synth.SCALE_MAX, bits=self.bits, fast=self.fast,
-                                       half_state=self.half_state, scratch=self.scratch, **self._ck(L))
-            else:   # the reference caller's three-call sequence (llama_adkv.py:263-276)
-                logits = gemv.forward_qk(q, L["kc"], k, *L["kp"], T, synth.SCALE_MIN, synth.SCALE_MAX,
-                                         bits=self.bits, fast=self.fast, half_state=self.half_state)
-                w = torch.softmax(logits.float() * self.scaling, dim=-1).to(torch.float16)
-                att = gemv.forward_ov(w, L["vc"], v, *L["vp"], synth.SCALE_MIN, synth.SCALE_MAX,
-                                      bits=self.bits, fast=self.fast, half_state=self.half_state)
-            x = x + self._allreduce(att.reshape(self.B, 1, -1) @ L["wo"].T)
-            x = x + self._mlp(L, _rms_norm(x, L["norm2"], self.s.norm_eps))
+            x = x + self._allreduce(self._attn_partial(L, x, T, cos, sin))
+            x = x + self._allreduce(self._mlp_partial(L, x))
         self.T = T + 1
-        last = _rms_norm(x[:, 0], self.final_norm, self.s.norm_eps)
-        return (last @ self.lm_head.T).argmax(-1)
+        return self._head(x)
 
 
-def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fused: bool = True, fast: bool = False,
+@torch.no_grad()
+def step_together(shards: list, ids: torch.Tensor) -> torch.Tensor:
+    """One decode step of tensor-parallel shards that live in one process (on one GPU): what every rank does in
+    :meth:`ADKVLlama.decode`, with each all-reduce replaced by the sum of the shards' partial results.  Used to
+    test the sharding (head slices of weights and ADKV parameters, caches per shard) without several GPUs."""
+    T = shards[0].T
+    cos, sin = shards[0].cos[T:T + 1], shards[0].sin[T:T + 1]
+    x = shards[0].embed[ids][:, None, :]
+    for li in range(len(shards[0].layers)):
+        x = x + torch.stack([m._attn_partial(m.layers[li], x, T, cos, sin) for m in shards]).sum(0)
+        x = x + torch.stack([m._mlp_partial(m.layers[li], x) for m in shards]).sum(0)
+    for m in shards:
+        m.T = T + 1
+    tok = shards[0]._head(x)
+    for m in shards[1:]:
+        m.last_logits = shards[0].last_logits
+    return tok
+
+
+@torch.no_grad()
+def prefill_together(shards: list, ids: torch.Tensor) -> torch.Tensor:
+    """Prefill of co-resident shards (see :func:`step_together`)."""
+    B, Tp = ids.shape
+    cos, sin = shards[0].cos[:Tp], shards[0].sin[:Tp]
+    x = shards[0].embed[ids]
+    for li in range(len(shards[0].layers)):
+        parts = []
+        for m in shards:
+            L = m.layers[li]
+            q, k, v = m._qkv(L, _rms_norm(x, L["norm1"], m.s.norm_eps), Tp)
+            q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
+            gemv.encode_kv_pair(L["kc"], k.contiguous(), L["kp"], L["vc"], v.contiguous(), L["vp"], synth.SCALE_MIN,
+                                synth.SCALE_MAX, bits=m.bits, half_state=m.half_state, **m._tails(L))
+            att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=m.hq != m.hkv)
+            parts.append(att.transpose(1, 2).reshape(B, Tp, -1) @ L["wo"].T)
+        x = x + torch.stack(parts).sum(0)
+        x = x + torch.stack([m._mlp_partial(m.layers[li], x) for m in shards]).sum(0)
+    for m in shards:
+        m.T = Tp
+    return shards[0]._head(x[:, -1:])
+
+
+def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fused: bool = True, fast: bool | None = None,
         ckpt_interval: int = 0, seed: int = 0, graph: bool = False, half_state: bool = False) -> dict:
     """Prefill a random prompt, generate `gen` tokens greedily; timings with CUDA events, max over ranks."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -297,7 +375,8 @@ def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fus
     return dict(rank=rank, world=world, prefill_ms=prefill_ms, decode_ms=decode_ms,
                 decode_tokens_per_s=batch * gen / (decode_ms * 1e-3), ms_per_decode_step=decode_ms / gen,
                 prefill_tokens_per_s=batch * prompt / (prefill_ms * 1e-3), device_status=status,
-                token_checksum=int(toks.sum().item()), tokens=toks)
+                token_checksum=int(toks.sum().item()), tokens=toks, fast=bool(model.fast),
+                tail_states=model.keeps_tails)
 
 
 def main():
@@ -308,20 +387,23 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--unfused", action="store_true")
-    ap.add_argument("--fast", action="store_true")
+    ap.add_argument("--fast", action="store_true", help="contracted replay even without tail states")
+    ap.add_argument("--exact", action="store_true", help="canonical replay even with tail states")
     ap.add_argument("--half-state", action="store_true",
                     help="the fp16-state arithmetic of the reference's CUDA kernels instead of the fp32 recurrence")
     ap.add_argument("--ckpt-interval", type=int, default=0)
     ap.add_argument("--graph", action="store_true", help="replay the decode step from a CUDA graph (device-side lengths)")
     a = ap.parse_args()
     shape = LlamaShape(n_layers=a.layers)
-    r = run(shape, a.batch, a.prompt, a.gen, bits=a.bits, fused=not a.unfused, fast=a.fast,
+    r = run(shape, a.batch, a.prompt, a.gen, bits=a.bits, fused=not a.unfused,
+            fast=True if a.fast else (False if a.exact else None),
             ckpt_interval=a.ckpt_interval, graph=a.graph, half_state=a.half_state)
     if r["rank"] == 0:
         r.pop("tokens")
         r.update(metric="e2e_decode_tokens_per_s", config=dict(model="random-init Llama-2-7B architecture", batch=a.batch,
                  prompt=a.prompt, generate=a.gen, layers=a.layers, bits=a.bits, fused=not a.unfused,
-                 replay="half" if a.half_state else ("fast" if a.fast else "exact"), tensor_parallel=r["world"],
+                 replay="half" if a.half_state else ("contracted" if r["fast"] else "canonical"),
+                 tail_states=r["tail_states"], tensor_parallel=r["world"],
                  cuda_graph=a.graph, data="synthetic"))
         print(json.dumps(r), flush=True)
     if dist.is_initialized():

@@ -349,10 +349,23 @@ def decode_scratch_bytes(B: int, Hq: int, Hkv: int, T: int, interval: int) -> in
     return n
 
 
+def _tails(k_tail, v_tail, B, H, D, half_state):
+    """Device pointers of the two tail states of a decode step (both or neither)."""
+    _require((k_tail is None) == (v_tail is None), "k_tail and v_tail go together")
+    _require(k_tail is None or not half_state, "tail states are for the fp32 arithmetic (half_state replays exactly)")
+    return _tail_ptr(k_tail, B, H, D), _tail_ptr(v_tail, B, H, D)
+
+
+def _fast_default(fast, k_tail) -> bool:
+    """Contracted replay unless the caller says otherwise, as soon as a tail state keeps the stored codes exact."""
+    return (k_tail is not None) if fast is None else bool(fast)
+
+
 def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
-                scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False,
+                scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool | None = None,
                 half_state: bool = False, out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None,
-                ckpt_interval: int = 0, scratch: torch.Tensor | None = None):
+                ckpt_interval: int = 0, scratch: torch.Tensor | None = None, k_tail: torch.Tensor | None = None,
+                v_tail: torch.Tensor | None = None, tail_keep: bool = False):
     """Fused decode step over both packed caches.
 
     ``q [B, nh_q, 1, DIM]``, ``k_new`` / ``v_new [B, nh_kv, 1, DIM]`` float16; ``k_params`` / ``v_params``
@@ -360,6 +373,13 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
     additive ``[B, T+1]`` (or ``[B, 1, T+1]`` / ``[B, 1, 1, T+1]``) tensor shared by all heads.  Appends to
     both caches in place as token ``T`` and returns ``softmax(q.K^T * scaling + mask) . V`` as
     ``[B, nh_q, DIM]`` float16, the appended token included (``src/adkv/hf/llama_adkv.py:263-276``).
+
+    ``k_tail`` / ``v_tail`` (float32 ``[B, nh_kv, 2, DIM]``, as written by :func:`encode_kv_pair` /
+    :func:`append_kv_pair` or left by the previous step): the recurrence state after token ``T-1``.  The reference
+    has no such state and quantises the new token with what its replay ends in (``src/adkv/kernel/gemv.cu:744-764``);
+    with the tails the new token is quantised from them -- bit-identical to the encoder -- and they advance to the
+    state after token ``T`` (``tail_keep=True``: left untouched, so that the same step can be repeated).  The replay
+    then only feeds the attention sums, and ``fast`` defaults to True (False without tails).
 
     With state checkpoints (``k_ckpt``, ``v_ckpt``, ``ckpt_interval``; see :func:`alloc_ckpt`) the token axis is
     processed in independent segments; ``scratch`` (uint8/any dtype, at least :func:`decode_scratch_bytes`) is
@@ -391,7 +411,8 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
     else:
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
-    flags = _lib.flags(fast, half_state)
+    kt, vt = _tails(k_tail, v_tail, B, Hkv, D, half_state)
+    flags = _lib.flags(_fast_default(fast, k_tail), half_state, tail_keep)
     with _on_device(k_cache.device):
         if ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, Hkv, D)
@@ -401,14 +422,14 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
             _require(scratch.is_cuda and scratch.is_contiguous(), "scratch must be a contiguous CUDA tensor")
             rc = _lib.load().adkv_decode_attn_ckpt(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                                                    kn.data_ptr(), vn.data_ptr(), ctypes.addressof(kp),
-                                                   ctypes.addressof(vp), kc, vc, iv, cap, mptr, mstride,
+                                                   ctypes.addressof(vp), kt, vt, kc, vc, iv, cap, mptr, mstride,
                                                    out.data_ptr(), scratch.data_ptr(),
                                                    scratch.numel() * scratch.element_size(), B, Hq, Hkv, T, D,
                                                    n_super_cap, bits, scaling, scale_min, scale_max, flags,
                                                    _stream(k_cache))
         else:
             rc = _lib.load().adkv_decode_attn(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
-                                              vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp), mptr,
+                                              vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp), kt, vt, mptr,
                                               mstride, out.data_ptr(), B, Hq, Hkv, T, D, n_super_cap, bits, scaling,
                                               scale_min, scale_max, flags, _stream(k_cache))
     _lib.check(rc, "decode_attn")
@@ -416,13 +437,14 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
 
 
 def decode_attn_varlen(q, k_cache, v_cache, k_new, v_new, k_params, v_params, seq_lens, scaling: float,
-                       scale_min, scale_max, *, bits: int = 4, fast: bool = False, half_state: bool = False,
-                       out: torch.Tensor | None = None):
+                       scale_min, scale_max, *, bits: int = 4, fast: bool | None = None, half_state: bool = False,
+                       out: torch.Tensor | None = None, k_tail: torch.Tensor | None = None,
+                       v_tail: torch.Tensor | None = None, tail_keep: bool = False):
     """Fused decode step with per-sequence lengths on the device.
 
     ``seq_lens`` int32 ``[B]`` CUDA tensor: sequence ``b`` attends over its ``seq_lens[b]`` cached tokens and
     appends the new token at that position (the caller advances ``seq_lens`` afterwards, on the device).
-    Otherwise as :func:`decode_attn` without a mask.  Nothing in the call depends on the lengths' values, so
+    Otherwise as :func:`decode_attn` without a mask (tail states included).  Nothing in the call depends on the lengths' values, so
     the same launch can be replayed step after step (e.g. from a captured CUDA graph)."""
     _require(q.dtype == torch.float16, "q must be float16")
     _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "k_new / v_new must be float16")
@@ -445,12 +467,14 @@ def decode_attn_varlen(q, k_cache, v_cache, k_new, v_new, k_params, v_params, se
     else:
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
+    kt, vt = _tails(k_tail, v_tail, B, Hkv, D, half_state)
     with _on_device(k_cache.device):
         rc = _lib.load().adkv_decode_attn_varlen(qc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kn.data_ptr(),
-                                                 vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp),
+                                                 vn.data_ptr(), ctypes.addressof(kp), ctypes.addressof(vp), kt, vt,
                                                  seq_lens.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, n_super_cap,
                                                  bits, scaling, scale_min, scale_max,
-                                                 _lib.flags(fast, half_state), _stream(k_cache))
+                                                 _lib.flags(_fast_default(fast, k_tail), half_state, tail_keep),
+                                                 _stream(k_cache))
     _lib.check(rc, "decode_attn_varlen")
     return out
 
@@ -460,7 +484,9 @@ STATIC_SCRATCH_BYTES = 16 << 20
 
 def decode_attn_static(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, scaling: float,
                        scale_min, scale_max, *, k_ckpt, v_ckpt, ckpt_interval: int, out: torch.Tensor,
-                       mask: torch.Tensor | None = None, bits: int = 4, fast: bool = False, half_state: bool = False):
+                       mask: torch.Tensor | None = None, bits: int = 4, fast: bool | None = None,
+                       half_state: bool = False, k_tail: torch.Tensor | None = None,
+                       v_tail: torch.Tensor | None = None, tail_keep: bool = False):
     """The checkpointed decode step for a caller that must not allocate device memory.
 
     Same arguments and result as ``decode_attn(..., k_ckpt=, v_ckpt=, ckpt_interval=)``, except that ``out``
@@ -496,12 +522,13 @@ def decode_attn_static(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T:
         _require(mask.dtype == torch.float32 and mask.is_cuda and mask.is_contiguous() and
                  tuple(mask.shape) == (B, T + 1), "mask must be a contiguous float32 [B, T + 1] CUDA tensor")
         mptr, mstride = mask.data_ptr(), T + 1
+    kt, vt = _tails(k_tail, v_tail, B, Hkv, D, half_state)
     with _on_device(k_cache.device):
         rc = _lib.load().adkv_decode_attn_ckpt_static(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
-            ctypes.addressof(kp), ctypes.addressof(vp), kc, vc, iv, cap, mptr, mstride, out.data_ptr(),
+            ctypes.addressof(kp), ctypes.addressof(vp), kt, vt, kc, vc, iv, cap, mptr, mstride, out.data_ptr(),
             B, Hq, Hkv, T, D, n_super_cap, bits, scaling, scale_min, scale_max,
-            _lib.flags(fast, half_state), _stream(k_cache))
+            _lib.flags(_fast_default(fast, k_tail), half_state, tail_keep), _stream(k_cache))
     _lib.check(rc, "decode_attn_static")
     return out
 

@@ -257,6 +257,8 @@ def build_gpu_state(w, seed, device, torch, ckpt_interval=0, half_state=False):
     kc = torch.zeros((B, Hkv, ns, D // 4, 4, 4), dtype=torch.uint8, device=device)
     vc = torch.zeros_like(kc)
     kck = vck = scratch = None
+    tk = torch.empty((B, Hkv, 2, D), dtype=torch.float32, device=device)
+    tv = torch.empty_like(tk)
     if ckpt_interval:
         kck = gemv.alloc_ckpt(B, Hkv, D, T + 1, ckpt_interval, device)
         vck = gemv.alloc_ckpt(B, Hkv, D, T + 1, ckpt_interval, device)
@@ -269,17 +271,17 @@ def build_gpu_state(w, seed, device, torch, ckpt_interval=0, half_state=False):
         if ckpt_interval:
             gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits,
                                 k_ckpt=kck[b0:b1], v_ckpt=vck[b0:b1], ckpt_interval=ckpt_interval,
-                                half_state=half_state)
+                                half_state=half_state, k_tail=tk[b0:b1], v_tail=tv[b0:b1])
         else:
             gemv.encode_kv_pair(kc[b0:b1], k, kp, vc[b0:b1], v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits,
-                                half_state=half_state)
+                                half_state=half_state, k_tail=tk[b0:b1], v_tail=tv[b0:b1])
         del k, v
     q = synth.gen_q(seed + 2, B, Hq, D, device=device)
     kn = synth.gen_kv(seed + 5, B, Hkv, 1, D, device=device, pos0=T)
     vn = synth.gen_kv(seed + 6, B, Hkv, 1, D, device=device, pos0=T)
     torch.cuda.synchronize(device)
     ck = dict(k_ckpt=kck, v_ckpt=vck, ckpt_interval=ckpt_interval, scratch=scratch) if ckpt_interval else {}
-    return dict(kc=kc, vc=vc, kp=kp, vp=vp, q=q, kn=kn, vn=vn, ck=ck)
+    return dict(kc=kc, vc=vc, kp=kp, vp=vp, q=q, kn=kn, vn=vn, ck=ck, tk=tk, tv=tv)
 
 
 def check_against_oracle(w, st, out, n_streams, torch):
@@ -521,12 +523,21 @@ def run_ours(args, w, name):
     ck = st["ck"]
     B, Hq, Hkv, D, T, bits = w["B"], w["Hq"], w["Hkv"], w["D"], w["T"], w["bits"]
     scaling = D ** -0.5
-    fast = args.replay == "fast"
     out = torch.empty((B, Hq, D), dtype=torch.float16, device=device)
+
+    def mode_kwargs(mode):
+        """Keyword arguments of gemv.decode_attn for a replay mode.  "tail": the new token is quantised from the
+        persisted tail state (bit-exact codes) and the cache is replayed in the contracted arithmetic; the tails
+        are kept as they are so that every timed step is the same step (token T appended at slot T)."""
+        if mode == "tail":
+            return dict(k_tail=st["tk"], v_tail=st["tv"], tail_keep=True)
+        return dict(fast=mode == "fast", half_state=mode == "half")
+
+    headline = mode_kwargs(args.replay)
 
     def step():
         gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, half_state=half, out=out, **ck)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, out=out, **headline, **ck)
 
     def barrier():
         if world > 1:
@@ -567,7 +578,7 @@ def run_ours(args, w, name):
         dk_.copy_(hk, non_blocking=True)
         dv_.copy_(hv, non_blocking=True)
         gemv.decode_attn(dq, st["kc"], st["vc"], dk_, dv_, st["kp"], st["vp"], T, scaling,
-                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=fast, half_state=half, out=out, **ck)
+                         synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, out=out, **headline, **ck)
         hout.copy_(out, non_blocking=True)
 
     for _ in range(max(3, min(args.warmup, 5))):
@@ -584,12 +595,12 @@ def run_ours(args, w, name):
     # the other replay arithmetics, same workload and caches, for the record (not the headline)
     others = []
     other_steps = max(1, min(args.steps, 50))
-    for mode in ("exact", "fast", "half"):
-        if mode == args.replay or ((mode == "half") != half and args.ckpt_interval):
-            continue     # checkpoints hold the states of the arithmetic the caches were written with
+    for mode in ("tail", "exact", "fast", "half"):
+        if mode == args.replay or ((mode == "half") != half and args.ckpt_interval) or (mode == "tail" and half):
+            continue     # checkpoints and tails hold the states of the arithmetic the caches were written with
         ms = time_cuda(lambda: gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], T,
-                                                scaling, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, fast=mode == "fast",
-                                                half_state=mode == "half", out=out, **ck),
+                                                scaling, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, out=out,
+                                                **mode_kwargs(mode), **ck),
                        torch, device, other_steps)
         others.append([mode, ms])
     # the three-call sequence of the reference's caller (src/adkv/hf/llama_adkv.py:263-276): unscaled logits,
@@ -605,7 +616,8 @@ def run_ours(args, w, name):
             return fn
         kc2, vc2 = st["kc"].clone(), st["vc"].clone()
         n_trio = max(1, min(args.steps, 20))
-        ms = time_cuda(trio(gemv.forward_qk, gemv.forward_ov, bits=bits, fast=fast, half_state=half), torch, device, n_trio)
+        ms = time_cuda(trio(gemv.forward_qk, gemv.forward_ov, bits=bits, fast=args.replay == "fast", half_state=half),
+                       torch, device, n_trio)
         trio_legs["unfused_trio"] = {"ms_per_step": ms, "value": algorithmic_bytes(w) / (ms * 1e-3) / 1e9, "unit": UNIT,
                                      "what": "forward_qk + torch softmax + forward_ov of this library"}
         ref = None if args.no_cpu else reference_cuda_module(w)     # a baseline leg, like the CPU one
@@ -683,9 +695,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
-    ap.add_argument("--replay", choices=["exact", "fast", "half"], default="exact",
-                    help="exact / fast: the fp32 recurrence (canonical order / contracted); half: the fp16-state "
-                         "arithmetic of the reference's CUDA kernels (ADKV_FLAG_HALF_STATE)")
+    ap.add_argument("--replay", choices=["tail", "exact", "fast", "half"], default="tail",
+                    help="tail: the fp32 recurrence with a persisted tail state (appended codes bit-exact, contracted "
+                         "replay); exact / fast: without tail state, replay in canonical order / contracted; half: the "
+                         "fp16-state arithmetic of the reference's CUDA kernels (ADKV_FLAG_HALF_STATE)")
     ap.add_argument("--ckpt-interval", type=int, default=0,
                     help="decode with state checkpoints every N tokens (segment-parallel kernel + merge)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define ADKV_ABI_VERSION 1
+#define ADKV_ABI_VERSION 2
 
 /* argument errors */
 #define ADKV_E_NULL      (-1)  /* a required pointer is NULL */
@@ -46,7 +46,8 @@ extern "C" {
 #define ADKV_E_START     (-7)  /* chunked encode: t_start given without a tail state */
 #define ADKV_E_SCRATCH   (-8)  /* the scratch memory given is smaller than the problem needs */
 #define ADKV_E_STATIC_MAX (-9) /* problem needs more than ADKV_STATIC_SCRATCH_BYTES of built-in scratch */
-#define ADKV_E_FLAGS     (-10) /* a flag is not available for this entry point (none at present) */
+#define ADKV_E_FLAGS     (-10) /* a flag or optional argument is not available in this combination (tail states with
+                                  ADKV_FLAG_HALF_STATE; only one of the two tail states given) */
 
 /* Size of the library's built-in scratch array (see adkv_decode_attn_ckpt_static). */
 #define ADKV_STATIC_SCRATCH_BYTES (16u << 20)
@@ -62,6 +63,10 @@ extern "C" {
  * error.  Takes precedence over ADKV_FLAG_FAST_REPLAY.  Available in every entry point that takes flags, for the
  * head dims that entry point serves. */
 #define ADKV_FLAG_HALF_STATE 2u
+/* Decode entry points with tail states: quantise the new token with the tail, but leave the tail as it is instead
+ * of advancing it over that token.  The call can then be repeated with the same T (the appended code overwrites
+ * itself): benchmarks that time one step over and over, and callers that may still reject the token. */
+#define ADKV_FLAG_TAIL_KEEP 4u
 
 /* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each
  * (src/adkv/hf/llama_adkv.py:27: zp_init, scale_init, alpha, beta, quant_target). */
@@ -143,20 +148,30 @@ int adkv_forward_ov(const void *attn, void *v_cache, const void *v_new, const ad
 /* Fused decode step: q.K^T, * scaling, + mask, softmax, P.V, both appends, one launch.  Replaces the
  * sequence forward_qk -> torch softmax -> forward_ov of src/adkv/hf/llama_adkv.py:263-276.
  *   mask float [B, T+1] additive, shared by all heads (row stride mask_stride_b elements), or NULL.
- *   out  fp16 [B, Hq, D]. */
+ *   out  fp16 [B, Hq, D].
+ *   k_tail, v_tail  float [B, Hkv, 2, D] (zp then scale), both or neither; in/out.  The reference keeps no
+ *          state between steps: its kernels replay the cache and quantise the new token with whatever state
+ *          the replay ends in (src/adkv/kernel/gemv.cu:744-764), which ties the replay to the encoder's exact
+ *          arithmetic.  With tail states -- the state after token T-1 as adkv_encode* / adkv_append* / the
+ *          previous decode step left it -- the new token is quantised from the tail (bit-identical to the
+ *          encoder, in O(1)), the tail advances to the state after token T, and the replay of tokens [0, T)
+ *          only feeds the attention sums, so ADKV_FLAG_FAST_REPLAY then costs no exactness of the stored codes.
+ *          Not available with ADKV_FLAG_HALF_STATE (ADKV_E_FLAGS): that arithmetic is the encoder's own. */
 int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                     const adkv_params *kp, const adkv_params *vp, const void *mask, long long mask_stride_b,
+                     const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail,
+                     const void *mask, long long mask_stride_b,
                      void *out, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
                      float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
 
-/* adkv_decode_attn with per-sequence token counts held on the device: seq_lens int32 [B]; sequence b attends
- * over its tokens [0, seq_lens[b]) and appends its new token at seq_lens[b].  No counterpart in the reference
+/* adkv_decode_attn (tail states as there) with per-sequence token counts held on the device: seq_lens int32 [B];
+ * sequence b attends over its tokens [0, seq_lens[b]) and appends its new token at seq_lens[b].  No counterpart in the reference
  * (one host integer T for the whole batch, src/adkv/kernel/gemv.py:25).  Serves ragged batches without padding
  * masks, and -- because no argument changes from step to step when the caller increments seq_lens on the
  * device -- a launch that is replayed unchanged.  A length that does not fit the cache cannot be rejected on
  * the host: that stream is skipped and adkv_device_status reports 6. */
 int adkv_decode_attn_varlen(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                            const adkv_params *kp, const adkv_params *vp, const void *seq_lens, void *out,
+                            const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail,
+                            const void *seq_lens, void *out,
                             int B, int Hq, int Hkv, int D, int n_super_cap, int bits, float scaling,
                             float scale_min, float scale_max, unsigned flags, void *stream);
 
@@ -184,9 +199,11 @@ long long adkv_decode_attn_ckpt_scratch_bytes(int B, int Hq, int Hkv, int T, int
 /* adkv_decode_attn over a checkpointed cache: one K/V warp pair per (stream, segment), partial results in
  * `scratch` (caller-owned device memory of at least adkv_decode_attn_ckpt_scratch_bytes, 16-byte aligned,
  * contents irrelevant on entry), then a merge kernel.  Appends token T to both caches and writes the
- * checkpoint when T completes an interval.  Same result as adkv_decode_attn up to fp32 summation order. */
+ * checkpoint when T completes an interval.  Same result as adkv_decode_attn up to fp32 summation order.
+ * k_tail / v_tail as in adkv_decode_attn; with them the checkpoint written is the advanced tail. */
 int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                          const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt, int interval,
+                          const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail,
+                          void *k_ckpt, void *v_ckpt, int interval,
                           int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out, void *scratch,
                           long long scratch_bytes, int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits,
                           float scaling, float scale_min, float scale_max, unsigned flags, void *stream);
@@ -206,7 +223,8 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
  *     needs clearing (every slot read is written first within the call), but two calls that overlap on the
  *     GPU -- different streams, or different host threads -- race on it: serialise them. */
 int adkv_decode_attn_ckpt_static(const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new,
-                                 const adkv_params *kp, const adkv_params *vp, void *k_ckpt, void *v_ckpt,
+                                 const adkv_params *kp, const adkv_params *vp, void *k_tail, void *v_tail,
+                                 void *k_ckpt, void *v_ckpt,
                                  int interval, int n_ckpt_cap, const void *mask, long long mask_stride_b, void *out,
                                  int B, int Hq, int Hkv, int T, int D, int n_super_cap, int bits, float scaling,
                                  float scale_min, float scale_max, unsigned flags, void *stream);

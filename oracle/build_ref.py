@@ -10,12 +10,23 @@ straight with nvcc / g++ (the reference's own build path is not run).  Output: `
 Python extension module exporting ``forward_qk``, ``forward_ov``, ``encode_kv`` (``gemv.cpp:28-33``).  No
 reference source is copied; the folder is git-ignored.
 
+The recipe also stages, byte for byte, the reference's Python files that the checkers execute -- its model
+file ``src/adkv/hf/llama_adkv.py`` (the caller of the three entry points), its torch recurrence
+``src/adkv/train/train_model.py`` (the CPU path) and the package ``__init__.py`` files above them -- into
+``oracle/_ref/src/``.  Like the ``.so`` they are build outputs: git-ignored, never edited, and they travel with
+the snapshot to the GPU box, where no reference checkout exists.  The reference's own ``adkv/kernel/gemv.py``
+(which JIT-builds its extension at import) is deliberately not staged: tests register ``adkv_b200.gemv`` under
+that module name instead (``adkv_b200.hf_shim``).
+
 Used only by tests (to pin the packed layout and the append / self-token semantics by executing the
-reference's kernels on the GPU) and by ``bench.py`` as a reported comparison.  The product never loads it.
+reference's kernels on the GPU, and to run the reference's unmodified model file on this library's kernels)
+and by ``bench.py`` as reported comparisons (the reference's CUDA kernels, its torch CPU path).  The product
+never loads any of it.
 """
 from __future__ import annotations
 
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
@@ -24,6 +35,29 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "adkv_gemv.so")
 NAME = "adkv_gemv"
+SRC_DIR = os.path.join(OUT_DIR, "src")
+# files executed by the checkers, relative to <reference>/src
+STAGED = ("adkv/__init__.py", "adkv/kernel/__init__.py", "adkv/hf/llama_adkv.py", "adkv/train/__init__.py",
+          "adkv/train/train_model.py")
+
+
+def stage_python(ref_root: str) -> str | None:
+    """Copy the STAGED files, unchanged, to oracle/_ref/src/.  Returns that folder, or None without a checkout."""
+    src = os.path.join(ref_root, "src")
+    if not os.path.exists(os.path.join(src, "adkv", "hf", "llama_adkv.py")):
+        return None
+    for rel in STAGED:
+        a, b = os.path.join(src, rel), os.path.join(SRC_DIR, rel)
+        if not os.path.exists(a):          # a package without __init__.py stays a namespace package
+            continue
+        os.makedirs(os.path.dirname(b), exist_ok=True)
+        shutil.copyfile(a, b)
+    return SRC_DIR
+
+
+def staged_src() -> str | None:
+    """The folder to put on sys.path to import the staged files as ``adkv.*``, if they have been staged."""
+    return SRC_DIR if os.path.exists(os.path.join(SRC_DIR, "adkv", "hf", "llama_adkv.py")) else None
 
 
 def build(ref_root: str, force: bool = False, verbose: bool = False) -> str | None:
@@ -32,6 +66,7 @@ def build(ref_root: str, force: bool = False, verbose: bool = False) -> str | No
     cu, cpp = os.path.join(kdir, "gemv.cu"), os.path.join(kdir, "gemv.cpp")
     if not (os.path.exists(cu) and os.path.exists(cpp)):
         return None
+    stage_python(ref_root)
     if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= max(os.path.getmtime(cu), os.path.getmtime(cpp)):
         return OUT
     import torch

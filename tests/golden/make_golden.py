@@ -2,7 +2,9 @@
 
 Run in a container that has the reference checkout (it is not needed to run the tests):
 
-    TORCH_COMPILE_DISABLE=1 python tests/golden/make_golden.py /path/to/reference
+    TORCH_COMPILE_DISABLE=1 python tests/golden/make_golden.py /path/to/reference [case ...]
+
+(no case names: all of them).
 
 The script imports ``adkv.train.train_model`` from ``<reference>/src`` unmodified and
 calls its ``_adkv_chunk_forward`` (``src/adkv/train/train_model.py:46-86``) eagerly
@@ -117,7 +119,37 @@ def main():
     p = tuple(t.half().float() if i != 1 else t for i, t in enumerate(p))
     cases["clamp_eps_ties_b4"] = run_case(tm, recorded, x.half(), p, 4, smin, smax)
 
+    # 5: case 4 with parameters the kernel API can take (fp16): the only fp16 value below the eps guard is 0.0
+    # (the smallest fp16 subnormal, 5.96e-8, is already above 1e-8).  Guard, both clamps and exact ties.
+    g5 = torch.Generator().manual_seed(55)
+    x = torch.zeros(1, H, 120, D)
+    x[..., 32:64] = torch.randn(1, H, 120, 32, generator=g5) * 500
+    x[..., 64:96] = torch.randn(1, H, 120, 32, generator=g5)
+    x[..., 96:] = torch.randn(1, H, 120, 32, generator=g5) * 0.01
+    x[0, 0, 0, 64:96] = ties
+    s0 = torch.ones(H, D)
+    s0[0, 96:] = 0.0
+    p = tuple(t.half().float() for t in (torch.zeros(H, D), s0, torch.full((H, D), 0.1), torch.full((H, D), 0.1),
+                                          torch.full((H, D), 3.5)))
+    cases["guard_clamp_ties_fp16_b4"] = run_case(tm, recorded, x.half(), p, 4, smin, smax)
+
+    # 6: scale_min = 0, so nothing holds the scale up: on all-zero and on tiny inputs it decays below the eps guard
+    # in mid-sequence (factor 1 - beta*target = 0.65 per token, 1e-8 after ~43 tokens) and the guard alone decides
+    # the quotient from then on; later tokens are large again, so the scale has to climb back out.
+    g6 = torch.Generator().manual_seed(66)
+    x = torch.zeros(1, H, 120, D)
+    x[..., 32:64] = torch.randn(1, H, 120, 32, generator=g6) * 3e-7      # fp16 subnormals
+    x[..., 64:96] = torch.randn(1, H, 120, 32, generator=g6) * 1e-4
+    x[..., 96:] = torch.randn(1, H, 120, 32, generator=g6)
+    x[:, :, 80:, :64] = torch.randn(1, H, 40, 64, generator=g6) * 2.0
+    p = tuple(t.half().float() for t in (torch.zeros(H, D), torch.ones(H, D), torch.full((H, D), 0.1),
+                                          torch.full((H, D), 0.1), torch.full((H, D), 3.5)))
+    cases["guard_decay_scale_min0_b4"] = run_case(tm, recorded, x.half(), p, 4, 0.0, smax)
+
+    only = set(sys.argv[2:])
     for name, d in cases.items():
+        if only and name not in only:
+            continue
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **d)
         print(name, {k: getattr(v, "shape", v) for k, v in d.items() if k in ("x", "codes")},

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/adkv_b200.h but not exported"
     assert set(names) == set(_lib.SIGNATURES), "ctypes signatures out of step with the header"
-    assert lib.adkv_abi_version() == 1
+    assert lib.adkv_abi_version() == 2
 
 
 def test_strerror_texts():
@@ -62,8 +62,14 @@ def test_null_and_shape_errors_from_the_c_abi():
     assert lib.adkv_encode(16, 16, pp, None, 1, 1, 4, 128, 1, 4, 4, 0.1, 1.0, None) == -7
     assert lib.adkv_forward_qk(16, 16, 16, pp, 16, 1, 3, 2, 4, 128, 1, 4, 0.1, 1.0, 0, None) == -4
     assert lib.adkv_forward_qk(16, 24, 16, pp, 16, 1, 2, 2, 4, 128, 1, 4, 0.1, 1.0, 0, None) == -6
-    assert lib.adkv_decode_attn(16, 16, 16, 16, 16, pp, pp, None, 0, 16, 1, 2, 2, 8, 128, 1, 4,
+    assert lib.adkv_decode_attn(16, 16, 16, 16, 16, pp, pp, None, None, None, 0, 16, 1, 2, 2, 8, 128, 1, 4,
                                 0.1, 0.1, 1.0, 0, None) == -5
+    # tail states: both or neither, and not with the fp16-state arithmetic
+    da = lambda kt, vt, flags: lib.adkv_decode_attn(16, 16, 16, 16, 16, pp, pp, kt, vt, None, 0, 16, 1, 2, 2, 7, 128,
+                                                    1, 4, 0.1, 0.1, 1.0, flags, None)
+    assert da(16, None, 0) == -10
+    assert da(16, 16, _lib.FLAG_HALF_STATE) == -10
+    assert da(16, 24, 0) == -6
 
 
 def test_argument_errors_of_the_flagged_entry_points():
