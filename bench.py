@@ -4,25 +4,32 @@
 
 A step is one fused decode-attention pass (q.K^T, softmax, P.V and both appends, one launch) over one
 batch of synthetic post-RoPE-outlier K/V held as packed ADKV codes.  The default workload is the
-Llama-2-7B shape of the headline metric: 32 heads, head_dim 128, batch 128 per GPU, 4096 cached
-tokens, 4-bit codes.  With N > 1 (one process per GPU, launched by torch.distributed.run) every rank
-runs the same per-GPU batch on its own shard of sequences (no data-path collective; weak scaling,
-``--scaling strong`` splits a fixed batch instead).  Rank 0 prints one JSON line.
+Llama-2-7B shape of the headline metric: 32 heads, head_dim 128, batch 128, 4096 cached tokens, 4-bit
+codes.  With N > 1 (one process per GPU, launched by torch.distributed.run) the (batch, kv-head) streams
+of that fixed workload are sharded over the ranks (``adkv_b200.sharding``: whole sequences first, KV heads
+when the batch does not divide) with no collective on the data path: strong scaling.  ``--scaling weak``
+gives every rank the whole workload instead; with the default the weak figure is measured too and printed
+as the extra key ``weak_scaling``.  Rank 0 prints one JSON line.
 
 ``value``  : packed-KV bytes processed per second by the whole job, inputs resident in HBM.
 ``e2e``    : the same through the public Python API with the step's q / k_new / v_new coming from
              pinned host memory and the output copied back, copies inside the timed region.
 ``roofline``: algorithmic bytes per launch / average launch time (CUDA events) against the measured
              HBM copy bandwidth of MEASURED_PEAKS.json.
-``cpu_baseline``: the C restatement of the reference algorithm (oracle/) on the host cores, on a
-             bounded sample of the same workload; also used to check the GPU result of the sample.
-             The baseline legs (this one and ``reference_cuda``) are the only code here that touches
-             oracle/, they run after the timed regions, and ``--no-cpu`` skips them.
-``--impl reference`` times that CPU implementation alone (the reference's torch path cannot travel to
-             the GPU box).
+``cpu_baseline``: the reference's own torch recurrence (staged unchanged under oracle/_ref/src by
+             oracle/build_ref.py) + torch attention on the host cores, on a bounded sample of the same
+             workload, and its time for the CPU-sized configuration (batch 1, 1024 tokens).  Where the staged
+             file is absent: the C restatement (``kind: "port"``).
+``cpu_baseline_port``: the C/OpenMP restatement of the same algorithm (oracle/), a much stricter CPU figure;
+             it also checks the GPU result of its sample (``parity_check``).
+             The baseline legs are the only code here that touches oracle/; they run after the timed
+             regions, and ``--no-cpu`` skips them.
+``--impl reference`` times the reference's CPU implementation alone, one bounded sample per step.
 ``reference_cuda``, ``unfused_trio``: for the record, the reference caller's three-call sequence
              (forward_qk, torch softmax, forward_ov) through the reference's own CUDA kernels recompiled for
              sm_100a (oracle/_ref, when built; they compute in fp16) and through this library's kernels.
+``other_workloads``: one-GPU figures of the prefill-quantise configuration (4- and 2-bit) and of the long-context
+             grouped-query configuration, a few steps each, so that one run records every benchmark shape.
 """
 from __future__ import annotations
 
@@ -91,7 +98,7 @@ def measured_peak_gbs():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML (read only) in a thread."""
 
-    def __init__(self, index: int, pci_bus_id: str | None = None, period_s: float = 0.02):
+    def __init__(self, index: int, pci_bus_id: str | None = None, period_s: float = 0.002):
         self.index, self.period = index, period_s
         self.samples, self.mark = [], None
         self._stop = threading.Event()
@@ -216,33 +223,139 @@ def pick_sample_streams(w, target_s: float) -> int:
     return max(thr, min(n, w["B"] * w["Hkv"]))
 
 
+def workload_config(name, w_rank, w_global, world, args) -> dict:
+    """The ``config`` object of the JSON line; both arms print the same one for the same command line."""
+    nbytes = algorithmic_bytes(w_rank)
+    return dict(workload=name, per_gpu=w_rank, global_batch=w_global["B"], replay=args.replay,
+                ckpt_interval=args.ckpt_interval,
+                sharding="(batch, kv-head) streams split over one process per GPU, no collective on the data path",
+                l2="inputs (packed K+V per step) larger than L2; no flush needed"
+                if nbytes > 200e6 else "inputs smaller than L2: cache-resident timing")
+
+
+def rank_workload(w, world, rank, scaling):
+    """The slice of workload ``w`` that rank ``rank`` of ``world`` owns: all of it for weak scaling, its rectangle
+    of the (batch, kv-head) grid for strong scaling."""
+    if world == 1 or scaling == "weak":
+        return dict(w)
+    from adkv_b200 import sharding
+    sh = sharding.plan(w["B"], w["Hkv"], world)[rank]
+    G = w["Hq"] // w["Hkv"]
+    return dict(w, B=sh.b1 - sh.b0, Hkv=sh.h1 - sh.h0, Hq=G * (sh.h1 - sh.h0))
+
+
+# ---- the reference's torch recurrence (oracle/_ref/src, staged unchanged) on the host cores
+
+def torch_reference_sample(w, n_seq: int, n_heads: int, tokens: int, seed: int = 4321):
+    """Inputs of ``n_seq`` sequences x ``n_heads`` KV heads of the workload, the first ``tokens + 1`` tokens."""
+    from adkv_b200 import synth
+    G, D, bits = w["Hq"] // w["Hkv"], w["D"], w["bits"]
+    return dict(k=synth.gen_kv(seed, n_seq, n_heads, tokens + 1, D), v=synth.gen_kv(seed + 1, n_seq, n_heads, tokens + 1, D),
+                q=synth.gen_q(seed + 2, n_seq, G * n_heads, D), kp=synth.gen_params(seed + 3, n_heads, D, bits),
+                vp=synth.gen_params(seed + 4, n_heads, D, bits), bits=bits, scaling=D ** -0.5, n_seq=n_seq,
+                n_heads=n_heads, tokens=tokens)
+
+
+def torch_reference_step(smp):
+    from adkv_b200 import synth
+    from oracle import ref_torch
+    return ref_torch.decode_attention(smp["q"], smp["k"], smp["v"], smp["kp"], smp["vp"], smp["bits"], smp["scaling"],
+                                      synth.SCALE_MIN, synth.SCALE_MAX)
+
+
+def pick_torch_sample(w, step_budget_s: float):
+    """(sequences, kv heads, tokens) of a sample whose step takes about ``step_budget_s`` on this host.  The
+    reference's recurrence is a Python loop over tokens (src/adkv/train/train_model.py:66-81), so its time is
+    tokens x (a fixed cost per token + a cost per channel): two probes give both."""
+    T, H = w["T"], w["Hkv"]
+    tp = min(T, 256)
+    t_small, _ = timed_cpu(lambda s=torch_reference_sample(w, 1, 1, tp): torch_reference_step(s))
+    t_wide, _ = timed_cpu(lambda s=torch_reference_sample(w, 1, H, tp): torch_reference_step(s))
+    per_tok_head = max((t_wide - t_small) / (tp * max(H - 1, 1)), 1e-9)
+    per_tok_fixed = max(t_small / tp - per_tok_head, 1e-9)
+    est = lambda heads, toks: toks * (per_tok_fixed + per_tok_head * heads)
+    if est(H, T) <= step_budget_s:                      # whole sequences
+        n_seq = int(max(1, min(w["B"], step_budget_s // est(H, T))))
+        return n_seq, H, T
+    heads = int(max(1, min(H, (step_budget_s / T - per_tok_fixed) / per_tok_head)))
+    if est(heads, T) <= step_budget_s * 1.5:
+        return 1, heads, T
+    return 1, 1, int(max(32, min(T, step_budget_s / (per_tok_fixed + per_tok_head))))
+
+
+def timed_cpu(fn, repeats: int = 1):
+    best, res = float("inf"), None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        res = fn()
+        best = min(best, time.perf_counter() - t0)
+    return best, res
+
+
+def torch_sample_bytes(w, smp) -> float:
+    """Algorithmic bytes of the part of the workload the sample stands for (tokens scaled linearly)."""
+    return sample_bytes(w, smp["n_seq"] * smp["n_heads"]) * (smp["tokens"] / w["T"])
+
+
+def describe_torch_sample(w, smp) -> str:
+    extra = "" if smp["tokens"] == w["T"] else f", first {smp['tokens']} of {w['T']} tokens (bytes scaled linearly)"
+    return (f"{smp['n_seq']} sequence(s) x {smp['n_heads']} of {w['Hkv']} kv heads = {smp['n_seq'] * smp['n_heads']} of "
+            f"{w['B'] * w['Hkv']} (batch, kv-head) streams per step{extra}; the reference's _adkv_chunk_forward "
+            "(eager) on K and V + torch attention")
+
+
+def config1_seconds():
+    """The reference's CPU-sized configuration (batch 1, 32 heads, 1024 tokens, head_dim 128, 4-bit): seconds for its
+    quantise -> dequantise -> single-query attention, best of 3."""
+    w1 = dict(B=1, Hq=32, Hkv=32, D=128, T=1023, bits=4)
+    smp = torch_reference_sample(w1, 1, 32, 1023)
+    return timed_cpu(lambda: torch_reference_step(smp), repeats=3)[0]
+
+
 def run_reference(args, w, name):
-    """The reference algorithm on the host cores (C restatement, all threads), bounded sample per step."""
+    """The reference's CPU implementation of the path on the host cores, one bounded sample per step: its own torch
+    recurrence where oracle/_ref/src holds it, else the C restatement (all threads)."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    from oracle import c_oracle
-    # size the per-step sample so that warm-up + timed steps take about a minute of host time
-    n = pick_sample_streams(w, target_s=min(2.0, max(0.05, 60.0 / (args.steps + args.warmup))))
-    s = cpu_sample(w, n)
+    import torch
+
+    from oracle import c_oracle, ref_torch
+    w_rank = rank_workload(w, world, 0, args.scaling)
+    budget = min(2.0, max(0.05, 120.0 / (args.steps + args.warmup)))
+    if ref_torch.available():
+        smp = torch_reference_sample(w, *pick_torch_sample(w, budget))
+        step = lambda: torch_reference_step(smp)
+        nbytes, sample = torch_sample_bytes(w, smp), describe_torch_sample(w, smp)
+        kind, cores = "reference", torch.get_num_threads()
+    else:
+        n = pick_sample_streams(w, target_s=budget)
+        s = cpu_sample(w, n)
+        step = lambda: cpu_step(w, s)
+        nbytes = sample_bytes(w, n)
+        sample = f"{n} of {w['B'] * w['Hkv']} (batch, kv-head) streams of the workload per step, C restatement with OpenMP"
+        kind, cores = "port", c_oracle.num_threads()
     for _ in range(args.warmup):
-        cpu_step(w, s)
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_step(w, s)
+        step()
     dt = time.perf_counter() - t0
-    val = sample_bytes(w, n) * args.steps / dt / 1e9
-    sample = f"{n} of {w['B'] * w['Hkv']} (batch, kv-head) streams of the workload per step"
-    print(json.dumps({
+    val = nbytes * args.steps / dt / 1e9
+    res = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": dict(workload=name, **w),
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": c_oracle.num_threads(), "kind": "port",
-                         "sample": sample},
+        "data": "synthetic", "config": workload_config(name, w_rank, w, world, args),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
+                         "host_cpus": os.cpu_count()},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }), flush=True)
+    }
+    if kind == "reference":
+        res["cpu_baseline"]["config1_seconds"] = config1_seconds()
+    print(json.dumps(res), flush=True)
 
 
 # --------------------------------------------------------------------------------------- GPU arm
@@ -500,6 +613,68 @@ def run_encode(args, w, name):
         sys.exit(1)
 
 
+def decode_ms(w, mode, torch, device, steps, seed=2000, ckpt_interval=0):
+    """Milliseconds per fused decode step of workload ``w`` on one GPU in replay mode ``mode`` (fresh state)."""
+    from adkv_b200 import gemv, synth
+    st = build_gpu_state(w, seed=seed, device=device, torch=torch, ckpt_interval=ckpt_interval)
+    out = torch.empty((w["B"], w["Hq"], w["D"]), dtype=torch.float16, device=device)
+    kw = dict(k_tail=st["tk"], v_tail=st["tv"], tail_keep=True) if mode == "tail" else dict(fast=mode == "fast")
+    ms = time_cuda(lambda: gemv.decode_attn(st["q"], st["kc"], st["vc"], st["kn"], st["vn"], st["kp"], st["vp"], w["T"],
+                                            w["D"] ** -0.5, synth.SCALE_MIN, synth.SCALE_MAX, bits=w["bits"], out=out,
+                                            **kw, **st["ck"]), torch, device, steps)
+    assert gemv.device_status(device) == 0, "a kernel gave up on a bounded wait"
+    return ms
+
+
+def encode_ms(w, torch, device, steps):
+    """Milliseconds per prefill-quantise step (K and V of one layer, one launch) and microseconds per appended
+    K+V token from the tail state, for an encode workload on one GPU."""
+    from adkv_b200 import gemv, synth
+    B, H, D, T, bits, A = w["B"], w["Hkv"], w["D"], w["T"], w["bits"], min(w["appends"], 32)
+    kp, vp = synth.gen_params(3, H, D, bits, device=device), synth.gen_params(4, H, D, bits, device=device)
+    k = torch.cat([synth.gen_kv(10 + b, 1, H, T, D, device=device) for b in range(B)])
+    v = torch.cat([synth.gen_kv(110 + b, 1, H, T, D, device=device) for b in range(B)])
+    ns = gemv.n_super_for(T + A, bits)
+    kc = torch.zeros((B, H, ns, D // 4, 4, 4), dtype=torch.uint8, device=device)
+    vc = torch.zeros_like(kc)
+    tk = torch.empty((B, H, 2, D), dtype=torch.float32, device=device)
+    tv = torch.empty_like(tk)
+    ms = time_cuda(lambda: gemv.encode_kv_pair(kc, k, kp, vc, v, vp, synth.SCALE_MIN, synth.SCALE_MAX, bits=bits,
+                                               k_tail=tk, v_tail=tv), torch, device, steps)
+    kn = synth.gen_kv(5, B, H, A, D, device=device, pos0=T)
+    vn = synth.gen_kv(6, B, H, A, D, device=device, pos0=T)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for i in range(A):
+        gemv.append_kv_pair(kc, kn[:, :, i:i + 1], kp, tk, vc, vn[:, :, i:i + 1], vp, tv, T + i, synth.SCALE_MIN,
+                            synth.SCALE_MAX, bits=bits)
+    a1.record()
+    torch.cuda.synchronize(device)
+    return ms, a0.elapsed_time(a1) * 1e3 / A
+
+
+def other_workload_figures(torch, device, peak):
+    """One-GPU figures of the benchmark shapes that are not the headline (a few steps each)."""
+    res = {}
+    for name in ("config3_prefill_b16_t8192_4bit", "config3_prefill_b16_t8192_2bit"):
+        w = WORKLOADS[name]
+        ms, app_us = encode_ms(w, torch, device, 5)
+        gbs = algorithmic_bytes(w) / (ms * 1e-3) / 1e9
+        res[name] = {"ms_per_layer_kv": ms, "value": gbs, "unit": UNIT, "frac_of_measured_peak": gbs / peak,
+                     "append_us_per_token_kv": app_us, "layers_in_the_configuration": 32}
+        torch.cuda.empty_cache()
+    name = "config5_llama3_8b_gqa_b32_t32768_2bit"
+    w = WORKLOADS[name]
+    leg = {}
+    for label, mode, iv in (("tail", "tail", 0), ("exact", "exact", 0), ("tail_ckpt2048", "tail", 2048)):
+        ms = decode_ms(w, mode, torch, device, 10, ckpt_interval=iv)
+        gbs = algorithmic_bytes(w) / (ms * 1e-3) / 1e9
+        leg[label] = {"ms_per_step": ms, "value": gbs, "unit": UNIT, "frac_of_measured_peak": gbs / peak}
+        torch.cuda.empty_cache()
+    res[name] = leg
+    return res
+
+
 def run_ours(args, w, name):
     import torch
     import torch.distributed as dist
@@ -513,10 +688,8 @@ def run_ours(args, w, name):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    w = dict(w)
-    if args.scaling == "strong" and world > 1:
-        assert w["B"] % world == 0, "strong scaling splits the batch evenly"
-        w["B"] //= world
+    w_global = dict(w)
+    w = rank_workload(w_global, world, rank, args.scaling)
     half = args.replay == "half"
     st = build_gpu_state(w, seed=1000 + 7919 * rank, device=device, torch=torch, ckpt_interval=args.ckpt_interval,
                          half_state=half)
@@ -631,17 +804,31 @@ def run_ours(args, w, name):
     step()                      # leave the caches and `out` as the headline arithmetic writes them
     torch.cuda.synchronize(device)
 
-    if world > 1:
-        t = torch.tensor([total_ms, e2e_ms] + [ms for _, ms in others], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = t.tolist()[:2]
-        others = [[m, v] for (m, _), v in zip(others, t.tolist()[2:])]
+    # the weak-scaling figure next to the strong one: every rank takes the whole workload
+    weak_ms = None
+    if world > 1 and args.scaling == "strong" and not args.no_weak:
+        weak_ms = decode_ms(w_global, args.replay if args.replay in ("tail", "exact", "fast") else "tail", torch, device,
+                            max(1, min(args.steps, 30)), seed=3000 + 7919 * rank, ckpt_interval=args.ckpt_interval)
 
     bytes_rank = algorithmic_bytes(w)
+    bytes_job = bytes_rank
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms, weak_ms or 0.0] + [ms for _, ms in others], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms, weak_ms = t.tolist()[:3]
+        others = [[m, v] for (m, _), v in zip(others, t.tolist()[3:])]
+        nb = torch.tensor([bytes_rank, B], dtype=torch.float64, device=device)
+        dist.all_reduce(nb, op=dist.ReduceOp.SUM)
+        bytes_job, seqs_job = nb.tolist()
+    else:
+        seqs_job = B
+    if args.scaling == "strong":
+        seqs_job = w_global["B"]            # kv-head shards of one sequence are not separate sequences
+
     res = None
     if rank == 0:
-        value = bytes_rank * world * args.steps / (total_ms * 1e-3) / 1e9
-        e2e_val = bytes_rank * world * args.steps / (e2e_ms * 1e-3) / 1e9
+        value = bytes_job * args.steps / (total_ms * 1e-3) / 1e9
+        e2e_val = bytes_job * args.steps / (e2e_ms * 1e-3) / 1e9
         peak, peak_src = measured_peak_gbs()
         avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
         achieved = bytes_rank / (avg_launch_ms * 1e-3) / 1e9
@@ -649,36 +836,52 @@ def run_ours(args, w, name):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict(workload=name, per_gpu=w, global_batch=w["B"] * world, replay=args.replay,
-                           ckpt_interval=args.ckpt_interval,
-                           sharding="batch, one process per GPU, no collective on the data path",
-                           l2="inputs (packed K+V per step) larger than L2; no flush needed"
-                           if bytes_rank > 200e6 else "inputs smaller than L2: cache-resident timing"),
+            "config": workload_config(name, w, w_global, world, args),
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": world * (hq.numel() + hk.numel() + hv.numel()) * 2,
                     "d2h_bytes_per_step": world * hout.numel() * 2, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": args.steps * (2 if args.ckpt_interval else 1),
-            "decode_tokens_per_s": {"one_layer": w["B"] * world * args.steps / (total_ms * 1e-3),
-                                    "over_32_layers": w["B"] * world * args.steps / (total_ms * 1e-3) / 32},
+            "decode_tokens_per_s": {"one_layer": seqs_job * args.steps / (total_ms * 1e-3),
+                                    "over_32_layers": seqs_job * args.steps / (total_ms * 1e-3) / 32},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "frac_of_8TBps_nominal": achieved / 8000.0,
-                         "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel": "decode_attn_kernel",
+                         "traffic": NCU_TRAFFIC_BYTES.get(name) if world == 1 else None, "kernel": "decode_attn_kernel",
                          "algorithmic_bytes_per_launch": bytes_rank, "avg_launch_ms": avg_launch_ms,
                          "median_launch_ms": statistics.median(per_launch_ms)},
             "clocks": sampler.summary(t_wall0, t_wall1),
-            "other_replay": [{"replay": m, "ms_per_step": ms, "value": bytes_rank * world / (ms * 1e-3) / 1e9,
+            "other_replay": [{"replay": m, "ms_per_step": ms, "value": bytes_job / (ms * 1e-3) / 1e9,
                               "unit": UNIT} for m, ms in others],
         }
+        if weak_ms:
+            wb = algorithmic_bytes(w_global) * world
+            res["weak_scaling"] = {"ms_per_step": weak_ms, "value": wb / (weak_ms * 1e-3) / 1e9, "unit": UNIT,
+                                   "global_batch": w_global["B"] * world,
+                                   "what": "every rank runs the whole workload (per-GPU work fixed)"}
         res.update(trio_legs)
         if world == 1 and not args.no_cpu and half:
             res["parity_check"] = "ok" if check_half(w, st, out) else "FAILED"
         elif world == 1 and not args.no_cpu:
             n = pick_sample_streams(w, target_s=args.cpu_seconds)
             ok, dt, n_used, cores = check_against_oracle(w, st, out, n, torch)
-            res["cpu_baseline"] = {"value": sample_bytes(w, n_used) / dt / 1e9, "unit": UNIT, "cores": cores,
-                                   "kind": "port", "seconds": dt,
-                                   "sample": f"{n_used} of {B * Hkv} (batch, kv-head) streams of the workload, "
+            port = {"value": sample_bytes(w, n_used) / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+                    "seconds": dt, "sample": f"{n_used} of {B * Hkv} (batch, kv-head) streams of the workload, "
                                              "one decode step, C restatement with OpenMP"}
             res["parity_check"] = "ok" if ok else "FAILED"
+            from oracle import ref_torch
+            if ref_torch.available():
+                # the reference's own torch path on the host cores: one sequence of the workload, best of 2
+                smp = torch_reference_sample(w, *pick_torch_sample(w, 6.0))
+                secs, want = timed_cpu(lambda: torch_reference_step(smp), repeats=2)
+                res["cpu_baseline"] = {"value": torch_sample_bytes(w, smp) / secs / 1e9, "unit": UNIT,
+                                       "cores": torch.get_num_threads(), "kind": "reference", "seconds": secs,
+                                       "sample": describe_torch_sample(w, smp), "host_cpus": os.cpu_count(),
+                                       "config1_seconds": config1_seconds()}
+                res["cpu_baseline_port"] = port
+            else:
+                res["cpu_baseline"] = port
+        if world == 1 and name == DEFAULT_WORKLOAD and not args.no_extra and not args.ckpt_interval:
+            del st
+            torch.cuda.empty_cache()
+            res["other_workloads"] = other_workload_figures(torch, device, peak)
         print(json.dumps(res), flush=True)
     if world > 1:
         dist.barrier()
@@ -694,7 +897,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
+                    help="strong (default): the workload is fixed and its streams are sharded over the GPUs; "
+                         "weak: every GPU runs the whole workload")
+    ap.add_argument("--no-weak", action="store_true", help="N > 1, strong scaling: skip the extra weak-scaling figure")
+    ap.add_argument("--no-extra", action="store_true", help="skip the figures of the other benchmark shapes")
     ap.add_argument("--replay", choices=["tail", "exact", "fast", "half"], default="tail",
                     help="tail: the fp32 recurrence with a persisted tail state (appended codes bit-exact, contracted "
                          "replay); exact / fast: without tail state, replay in canonical order / contracted; half: the "

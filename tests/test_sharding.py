@@ -94,3 +94,27 @@ def test_two_ranks_concatenate_to_single_rank_result(B, Hq, Hkv, bits):
     want = orc.decode_attn(q[:, :, 0].numpy(), kc, vc, k[:, :, T].numpy(), v[:, :, T].numpy(), kp, vp, T, 0.1, bits=bits)
     assert np.array_equal(ret["full"], want)
     assert ret["tmax"] == float(world)
+
+
+def test_bench_shards_the_fixed_workload_over_ranks():
+    """bench.py --gpus N: strong scaling splits the benchmark shapes with sharding.plan (whole sequences first, KV
+    heads when the batch does not divide); weak scaling gives every rank the whole workload; both arms print the
+    same config object."""
+    import argparse
+
+    import bench
+    w2 = bench.WORKLOADS["config2_llama2_7b_b128_t4096_4bit"]
+    w5 = bench.WORKLOADS["config5_llama3_8b_gqa_b32_t32768_2bit"]
+    for world in (1, 2, 4, 8):
+        parts = [bench.rank_workload(w2, world, r, "strong") for r in range(world)]
+        assert all(p["B"] == 128 // world and p["Hkv"] == 32 and p["Hq"] == 32 for p in parts)
+        assert bench.rank_workload(w2, world, 0, "weak") == w2
+        parts = [bench.rank_workload(w5, world, r, "strong") for r in range(world)]
+        assert sum(p["B"] * p["Hkv"] for p in parts) == 32 * 8 and all(p["Hq"] == 4 * p["Hkv"] for p in parts)
+    small = dict(w5, B=2)                                  # 2 sequences on 8 GPUs: the KV heads are split as well
+    parts = [bench.rank_workload(small, 8, r, "strong") for r in range(8)]
+    assert all(p["B"] == 1 and p["Hkv"] == 2 and p["Hq"] == 8 for p in parts)
+    args = argparse.Namespace(replay="tail", ckpt_interval=0)
+    a = bench.workload_config("x", parts[0], small, 8, args)
+    assert a == bench.workload_config("x", bench.rank_workload(small, 8, 0, "strong"), small, 8, args)
+    assert a["global_batch"] == 2 and a["per_gpu"]["Hkv"] == 2
