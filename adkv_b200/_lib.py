@@ -16,12 +16,17 @@ c_void_p, c_int, c_float, c_uint, c_longlong = (ctypes.c_void_p, ctypes.c_int, c
 FLAG_FAST_REPLAY = 1
 FLAG_HALF_STATE = 2
 FLAG_TAIL_KEEP = 4
+FLAG_SPLIT_CHANNELS = 8
+FLAG_NO_SPLIT_CHANNELS = 16
 ABI_VERSION = 2
 
 
-def flags(fast: bool = False, half_state: bool = False, tail_keep: bool = False) -> int:
+def flags(fast: bool = False, half_state: bool = False, tail_keep: bool = False,
+          split_channels: bool | None = None) -> int:
+    """``split_channels``: None = the library decides from the size of the launch."""
     return (FLAG_FAST_REPLAY if fast else 0) | (FLAG_HALF_STATE if half_state else 0) | \
-        (FLAG_TAIL_KEEP if tail_keep else 0)
+        (FLAG_TAIL_KEEP if tail_keep else 0) | \
+        (0 if split_channels is None else FLAG_SPLIT_CHANNELS if split_channels else FLAG_NO_SPLIT_CHANNELS)
 
 # name -> argument types (return type is int unless listed in _RESTYPE); mirrors include/adkv_b200.h
 SIGNATURES = {

@@ -16,8 +16,9 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libadkv_b200.so")
 SOURCES = ["adkv_capi.cu", "adkv_encode.cu", "adkv_fused.cu", "adkv_unfused.cu", "adkv_split.cu", "adkv_wide.cu",
-           "adkv_half.cu"]
+           "adkv_half.cu", "adkv_narrow.cu"]
 HEADERS = ["adkv_device.cuh", "adkv_decode.cuh", "adkv_softmax.cuh", "adkv_half.cuh", "adkv_io.cuh", "adkv_host.h",
+           "adkv_narrow.cuh",
            os.path.join("..", "..", "include", "adkv_b200.h")]
 OBJ_DIR = os.path.join(PKG, "build")
 

@@ -8,6 +8,7 @@ ADKV_HIDDEN int adkv_tu_status_encode(int *out);
 ADKV_HIDDEN int adkv_tu_status_split(int *out);
 ADKV_HIDDEN int adkv_tu_status_wide(int *out);
 ADKV_HIDDEN int adkv_tu_status_half(int *out);
+ADKV_HIDDEN int adkv_tu_status_narrow(int *out);
 
 namespace adkv {
 
@@ -59,7 +60,7 @@ int adkv_device_status(int *status, void *stream)
     if (!status) return ADKV_E_NULL;
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return int(e);
-    int a = 0, b = 0, c = 0, d = 0, w = 0, t = 0, hf = 0;
+    int a = 0, b = 0, c = 0, d = 0, w = 0, t = 0, hf = 0, nr = 0;
     if (int rc = adkv_tu_status_fused(&a)) return rc;
     if (int rc = adkv_tu_status_unfused(&b)) return rc;
     if (int rc = adkv_tu_status_encode(&c)) return rc;
@@ -67,7 +68,8 @@ int adkv_device_status(int *status, void *stream)
     if (int rc = adkv_tu_status_wide(&w)) return rc;
     if (int rc = adkv_tu_status_capi(&t)) return rc;
     if (int rc = adkv_tu_status_half(&hf)) return rc;
-    *status = a ? a : (b ? b : (c ? c : (d ? d : (w ? w : (hf ? hf : t)))));
+    if (int rc = adkv_tu_status_narrow(&nr)) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : (w ? w : (hf ? hf : (nr ? nr : t))))));
     return 0;
 }
 

@@ -61,8 +61,16 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
 
 using namespace adkv;
 
+// adkv_decode_attn splits the channels of a head over two warp pairs up to this many (batch, kv head) streams per
+// launch: measured on a B200 (4096 tokens, 4-bit) the split wins only while there is at most about one stream per
+// SM (128 streams: 200 us against 216 us); from 256 streams on the whole-head kernel is faster (512 streams:
+// 274 us against 324 us), because the split costs a quarter more instructions and both are then bound by issue.
+constexpr long long kSplitChannelsMaxStreams = 160;
+
 ADKV_HIDDEN int adkv_half_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
                                       float scaling, int B, int bits, const int *seq_lens, cudaStream_t s);
+ADKV_HIDDEN int adkv_narrow_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
+                                        float scaling, int B, int bits, bool exact, cudaStream_t s);
 ADKV_HIDDEN int adkv_wide_decode_attn(const KArgs &ka, const VArgs &va, const float *mask, long long mask_stride_b,
                                       float scaling, int B, int bits, int mode, cudaStream_t s);
 
@@ -97,6 +105,11 @@ int adkv_decode_attn(const void *q, void *k_cache, void *v_cache, const void *k_
                                      half ? 2 : int(exact), s);
     if (half)
         return adkv_half_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, nullptr, s);
+    // Very few streams: split every head over two warp pairs (adkv_narrow.cu).
+    const bool split = (flags & ADKV_FLAG_SPLIT_CHANNELS) ||
+                       (!(flags & ADKV_FLAG_NO_SPLIT_CHANNELS) && (long long)B * Hkv <= kSplitChannelsMaxStreams);
+    if (split)
+        return adkv_narrow_decode_attn(ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, B, bits, exact, s);
     ADKV_DISPATCH(bits, exact, Hq / Hkv,
                   (decode_attn_kernel<BITS, G, ARITH><<<B * Hkv, 64, 0, s>>>(
                       ka, va, static_cast<const float *>(mask), mask_stride_b, scaling, nullptr)))

@@ -71,7 +71,8 @@ class ADKVLlama:
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, bits: int = 4, device="cuda",
                  rank: int = 0, world: int = 1, seed: int = 0, fused: bool = True, fast: bool | None = None,
-                 ckpt_interval: int = 0, half_state: bool = False, peers: list | None = None):
+                 ckpt_interval: int = 0, half_state: bool = False, peers: list | None = None,
+                 split_channels: bool | None = None):
         """``fast``: None = contracted replay wherever tail states keep the stored codes exact (the fused step in the
         fp32 arithmetic), canonical replay otherwise.  ``peers``: the other tensor-parallel shards when all of them
         live in this process (tests on one GPU); the all-reduce is then a sum over the shards' partial results, and
@@ -83,6 +84,7 @@ class ADKVLlama:
         self.keeps_tails = fused and not half_state
         self.fast = self.keeps_tails if fast is None else fast
         self.peers = peers
+        self.split_channels = split_channels      # layout of a head over warps in the eager fused step (None: automatic)
         self.hq, self.hkv, self.ffn = shape.n_heads // world, shape.n_kv_heads // world, shape.ffn // world
         D, dm = shape.head_dim, shape.d_model
         g = torch.Generator(device=self.dev)
@@ -208,7 +210,7 @@ class ADKVLlama:
         elif self.fused:
             att = gemv.decode_attn(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], T, self.scaling, smin, smax,
                                    bits=self.bits, fast=self.fast, half_state=self.half_state, scratch=self.scratch,
-                                   **self._tails(L), **self._ck(L))
+                                   split_channels=self.split_channels, **self._tails(L), **self._ck(L))
         else:   # the reference caller's three-call sequence (llama_adkv.py:263-276)
             logits = gemv.forward_qk(q, L["kc"], k, *L["kp"], T, smin, smax, bits=self.bits, fast=self.fast,
                                      half_state=self.half_state)

@@ -365,7 +365,7 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
                 scale_min, scale_max, *, mask: torch.Tensor | None = None, bits: int = 4, fast: bool | None = None,
                 half_state: bool = False, out: torch.Tensor | None = None, k_ckpt=None, v_ckpt=None,
                 ckpt_interval: int = 0, scratch: torch.Tensor | None = None, k_tail: torch.Tensor | None = None,
-                v_tail: torch.Tensor | None = None, tail_keep: bool = False):
+                v_tail: torch.Tensor | None = None, tail_keep: bool = False, split_channels: bool | None = None):
     """Fused decode step over both packed caches.
 
     ``q [B, nh_q, 1, DIM]``, ``k_new`` / ``v_new [B, nh_kv, 1, DIM]`` float16; ``k_params`` / ``v_params``
@@ -383,7 +383,11 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
 
     With state checkpoints (``k_ckpt``, ``v_ckpt``, ``ckpt_interval``; see :func:`alloc_ckpt`) the token axis is
     processed in independent segments; ``scratch`` (uint8/any dtype, at least :func:`decode_scratch_bytes`) is
-    allocated per call when not given."""
+    allocated per call when not given.
+
+    ``split_channels``: None lets the library choose between one warp per tensor and stream and a head split
+    over two warp pairs (launches with few streams); True / False force one (head dim 128, fp32 arithmetic,
+    no checkpoints)."""
     _require(q.dtype == torch.float16, "q must be float16")
     _require(k_new.dtype == torch.float16 and v_new.dtype == torch.float16, "k_new / v_new must be float16")
     B, Hkv, n_super_cap, D = _cache_dims(k_cache, "k_cache")
@@ -412,7 +416,7 @@ def decode_attn(q, k_cache, v_cache, k_new, v_new, k_params, v_params, T: int, s
         _require(out.dtype == torch.float16 and out.is_contiguous() and out.shape == (B, Hq, D),
                  "out must be contiguous float16 [B, nh_q, DIM]")
     kt, vt = _tails(k_tail, v_tail, B, Hkv, D, half_state)
-    flags = _lib.flags(_fast_default(fast, k_tail), half_state, tail_keep)
+    flags = _lib.flags(_fast_default(fast, k_tail), half_state, tail_keep, split_channels)
     with _on_device(k_cache.device):
         if ckpt_interval:
             kc, vc, iv, cap = _ckpt_args(k_ckpt, v_ckpt, ckpt_interval, B, Hkv, D)

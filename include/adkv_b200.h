@@ -67,6 +67,13 @@ extern "C" {
  * of advancing it over that token.  The call can then be repeated with the same T (the appended code overwrites
  * itself): benchmarks that time one step over and over, and callers that may still reject the token. */
 #define ADKV_FLAG_TAIL_KEEP 4u
+/* adkv_decode_attn, head dim 128, fp32 arithmetic: how the channels of a head are laid over warps.  By default the
+ * library decides from the number of (batch, kv head) streams of the call: a launch with very few streams (about
+ * one per SM or fewer) splits every head over two K warps and two V warps so that the GPU has more warps to
+ * interleave; larger launches keep one warp per tensor and stream, which needs fewer instructions in all.  Results agree up to the summation order of the logits.  These two flags force one
+ * or the other (tests, tuning); with both set, SPLIT wins. */
+#define ADKV_FLAG_SPLIT_CHANNELS 8u
+#define ADKV_FLAG_NO_SPLIT_CHANNELS 16u
 
 /* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each
  * (src/adkv/hf/llama_adkv.py:27: zp_init, scale_init, alpha, beta, quant_target). */

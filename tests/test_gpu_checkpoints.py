@@ -50,7 +50,7 @@ def test_checkpointed_generation_matches_plain(bits, Hq, Hkv, T0, steps, S):
         o1 = gemv.decode_attn(q, k1, v1, kn, vn, kp, vp, T, 0.09, SMIN, SMAX, bits=bits, mask=m)
         o2 = gemv.decode_attn(q, k2, v2, kn, vn, kp, vp, T, 0.09, SMIN, SMAX, bits=bits, mask=m,
                               k_ckpt=kck, v_ckpt=vck, ckpt_interval=S)
-        torch.testing.assert_close(o2.float(), o1.float(), rtol=RTOL, atol=ATOL * max(1.0, float(o1.abs().max())))
+        torch.testing.assert_close(o2.float(), o1.float(), rtol=RTOL, atol=ATOL)
     assert gemv.device_status() == 0
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
     # every checkpoint reached equals the oracle's state at that token, bit for bit

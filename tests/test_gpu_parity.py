@@ -12,7 +12,9 @@ from tests.util import SMAX, SMIN, code_mismatch, dev, make_case, np_params, ora
 
 pytestmark = pytest.mark.gpu
 
-# north_star tolerance for fp16 attention outputs
+# tolerance stated for fp16 attention outputs (|got - want| <= 2e-3 + 2e-3 |want|), applied as it stands to the
+# outputs of decode_attn / forward_ov.  Only the unscaled fp16 logits of forward_qk get an absolute term scaled by
+# their magnitude: they are not normalised, and half an fp16 ulp of a logit of size L is already L * 4.9e-4.
 RTOL, ATOL = 2e-3, 2e-3
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
 
@@ -44,15 +46,29 @@ def test_encode_bit_exact(bits, T):
     assert np.array_equal(t[:, :, 1].view(np.uint32), st.s.view(np.uint32))
 
 
-@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+_PARAM_NAMES = ("zp_init", "scale_init", "alpha", "beta", "target")
+
+
+def _fp16_parameters(path) -> bool:
+    """The kernel API takes fp16 parameters (as the reference's model file stores them): a fixture can go through the
+    kernel only if its parameters are fp16 values.  (One fixture holds a scale_init of 1e-9 for the oracle's sake; its
+    fp16 counterpart, with 0.0 as the only value below the guard, is guard_clamp_ties_fp16_b4.)"""
+    d = np.load(path)
+    return all(np.array_equal(d[k].astype(np.float16).astype(np.float32), d[k]) for k in _PARAM_NAMES)
+
+
+GOLDEN_FP16 = [p for p in GOLDEN if _fp16_parameters(p)]
+
+
+@pytest.mark.parametrize("path", GOLDEN_FP16, ids=[os.path.basename(p) for p in GOLDEN_FP16])
 def test_encode_reproduces_reference_fixtures(path):
-    """Codes written by the kernel equal the codes the reference's torch code produced."""
+    """Codes written by the kernel equal the codes the reference's torch code produced: benchmark data, random
+    parameters, and the two guard fixtures (eps guard from a zero initial scale, both clamps, exact .5 ties; scale
+    decaying under the guard with scale_min = 0)."""
     d = np.load(path)
     bits = int(d["bits"])
-    names = ("zp_init", "scale_init", "alpha", "beta", "target")
+    names = _PARAM_NAMES
     p16 = tuple(torch.from_numpy(d[k]).half() for k in names)
-    if any(not torch.equal(a.float(), torch.from_numpy(d[k])) for a, k in zip(p16, names)):
-        pytest.skip("fixture parameters are not fp16-representable (the kernel API takes fp16 parameters)")
     x = torch.from_numpy(d["x"])
     B, H, T, D = x.shape
     cache = torch.zeros(orc.cache_shape(B, H, orc.n_super_for(T, bits), D), dtype=torch.uint8, device="cuda")
@@ -131,8 +147,9 @@ def test_forward_qk(B, Hq, Hkv, T, bits, fast):
     if not fast:
         assert np.array_equal(cache.cpu().numpy(), want_cache)          # appended code bit-exact
     else:
+        # only the appended token can differ: at most one in 1e-4 of its codes (and one code at these sizes)
         frac, dmax = code_mismatch(cache.cpu().numpy(), want_cache, T + 1, bits)
-        assert dmax <= 1 and frac <= 1e-4 + 2.0 / (B * Hkv * 128 * (T + 1))
+        assert dmax <= 1 and frac * B * Hkv * 128 * (T + 1) <= 1 + 1e-4 * B * Hkv * 128
 
 
 @pytest.mark.parametrize("fast", [False, True], ids=["exact", "fast"])
@@ -150,18 +167,20 @@ def test_forward_ov(B, Hq, Hkv, T, bits, fast):
                           bits=bits, fast=fast)
     _status_ok()
     assert got.shape == (B, Hq, 128) and got.dtype == torch.float16
-    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     if not fast:
         assert np.array_equal(cache.cpu().numpy(), want_cache)
     else:
+        # only the appended token can differ: at most one in 1e-4 of its codes (and one code at these sizes)
         frac, dmax = code_mismatch(cache.cpu().numpy(), want_cache, T + 1, bits)
-        assert dmax <= 1 and frac <= 1e-4 + 2.0 / (B * Hkv * 128 * (T + 1))
+        assert dmax <= 1 and frac * B * Hkv * 128 * (T + 1) <= 1 + 1e-4 * B * Hkv * 128
 
 
+@pytest.mark.parametrize("split", [False, True], ids=["whole_head", "split_head"])
 @pytest.mark.parametrize("fast", [False, True], ids=["exact", "fast"])
 @pytest.mark.parametrize("with_mask", [False, True], ids=["nomask", "mask"])
 @pytest.mark.parametrize("B,Hq,Hkv,T,bits", CASES)
-def test_decode_attn(B, Hq, Hkv, T, bits, with_mask, fast):
+def test_decode_attn(B, Hq, Hkv, T, bits, with_mask, fast, split):
     case = make_case(300 + T, B, Hq, Hkv, T, bits, outlier_mode="persistent" if T % 3 == 0 else "scale")
     kc, vc = oracle_prefill(case)
     mask = None
@@ -178,16 +197,21 @@ def test_decode_attn(B, Hq, Hkv, T, bits, with_mask, fast):
     dk, dv = dev(kc), dev(vc)
     got = gemv.decode_attn(dev(case["q"]), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
                            dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX,
-                           mask=None if mask is None else dev(mask), bits=bits, fast=fast)
+                           mask=None if mask is None else dev(mask), bits=bits, fast=fast, split_channels=split)
     _status_ok()
     assert got.shape == (B, Hq, 128) and got.dtype == torch.float16
-    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     if not fast:
         assert np.array_equal(dk.cpu().numpy(), wk) and np.array_equal(dv.cpu().numpy(), wv)
+    else:       # contracted replay without a tail state: the appended code may be off by one step, rarely
+        for a, b in ((dk.cpu().numpy(), wk), (dv.cpu().numpy(), wv)):
+            frac, dmax = code_mismatch(a, b, T + 1, bits)
+            assert dmax <= 1 and frac * B * Hkv * 128 * (T + 1) <= 1 + 1e-4 * B * Hkv * 128
 
 
+@pytest.mark.parametrize("split", [False, True], ids=["whole_head", "split_head"])
 @pytest.mark.parametrize("bits", [4, 2])
-def test_decode_with_scales_at_both_clamps(bits):
+def test_decode_with_scales_at_both_clamps(bits, split):
     """Channels whose scale sits at scale_min (all-zero input) or scale_max (saturating input) during the
     replay: the kernels' unguarded fast body must hand over to the guarded one without changing a bit."""
     B, H, T, D = 2, 2, 333, 128
@@ -208,9 +232,9 @@ def test_decode_with_scales_at_both_clamps(bits):
     assert np.isclose(st.s.min(), SMIN) and np.isclose(st.s.max(), SMAX)      # both clamps really are active
     dk, dv = dev(kc), dev(vc)
     got = gemv.decode_attn(dev(case["q"]), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
-                           dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits)
+                           dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits, split_channels=split)
     _status_ok()
-    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     assert np.array_equal(dk.cpu().numpy(), wk) and np.array_equal(dv.cpu().numpy(), wv)
 
 
@@ -236,7 +260,7 @@ def test_decode_varlen_ragged_batch(bits, Hq, Hkv):
     got = gemv.decode_attn_varlen(q, kc, vc, kn, vn, kp, vp, sl, 0.09, SMIN, SMAX, bits=bits)
     for b, T in enumerate(lens):
         want = gemv.decode_attn(q[b:b + 1], k_ref[b:b + 1], v_ref[b:b + 1], kn[b:b + 1], vn[b:b + 1], kp, vp, T, 0.09,
-                                SMIN, SMAX, bits=bits)
+                                SMIN, SMAX, bits=bits, split_channels=False)     # same kernel layout: bit-equal
         assert torch.equal(got[b:b + 1], want)
     assert torch.equal(kc, k_ref) and torch.equal(vc, v_ref)
     _status_ok()
@@ -277,7 +301,7 @@ def test_decode_with_infinite_mask_entries():
         _status_ok()
         g = got.float().cpu().numpy()
         assert np.isfinite(g).all()
-        np.testing.assert_allclose(g, want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+        np.testing.assert_allclose(g, want, rtol=RTOL, atol=ATOL)
 
 
 def test_decode_steps_chain_like_generation():
@@ -300,7 +324,7 @@ def test_decode_steps_chain_like_generation():
                                scale_min=SMIN, scale_max=SMAX)
         got = gemv.decode_attn(dev(q), dk, dv, dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1]),
                                kp, vp, T, 0.1, SMIN, SMAX, bits=bits)
-        np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+        np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     _status_ok()
     assert np.array_equal(dk.cpu().numpy(), ok_) and np.array_equal(dv.cpu().numpy(), ov_)
 
@@ -350,7 +374,7 @@ def test_full_size_config2_properties():
         _status_ok()
         got = out.float().cpu().numpy().reshape(B // R, R, H, D)
         assert np.array_equal(got, np.broadcast_to(got[0], got.shape))        # replicas agree bit for bit
-        np.testing.assert_allclose(got[0], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+        np.testing.assert_allclose(got[0], want, rtol=RTOL, atol=ATOL)
         if not fast:
             assert np.array_equal(dk[:R].cpu().numpy(), kc) and np.array_equal(dv[-R:].cpu().numpy(), vc)
         else:
@@ -384,14 +408,14 @@ def test_full_size_config5_gqa_2bit_properties():
     _status_ok()
     got = out.float().cpu().numpy()
     assert np.array_equal(got, np.broadcast_to(got[:1], got.shape))
-    np.testing.assert_allclose(got[:1], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    np.testing.assert_allclose(got[:1], want, rtol=RTOL, atol=ATOL)
     assert np.array_equal(dk[:1].cpu().numpy(), kc) and np.array_equal(dv[-1:].cpu().numpy(), vc)
     assert torch.equal(dk[0], dk[-1]) and torch.equal(dv[0], dv[-1])
     # contracted replay over 32768 tokens: output within tolerance, appended codes within the 1e-4 allowance
     out_f = gemv.decode_attn(rep(case["q"]), dk, dv, rep(case["k"][:, :, T:T + 1]), rep(case["v"][:, :, T:T + 1]),
                              dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits, fast=True)
     _status_ok()
-    np.testing.assert_allclose(out_f.float().cpu().numpy()[:1], want, rtol=RTOL, atol=ATOL * max(1.0, np.abs(want).max()))
+    np.testing.assert_allclose(out_f.float().cpu().numpy()[:1], want, rtol=RTOL, atol=ATOL)
     for got_c, want_c in ((dk[:1].cpu().numpy(), kc), (dv[:1].cpu().numpy(), vc)):
         a = orc.unpack_codes(got_c, T + 1, bits)[:, :, T].astype(np.int32)
         b = orc.unpack_codes(want_c, T + 1, bits)[:, :, T].astype(np.int32)

@@ -59,8 +59,9 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("split", [False, True], ids=["whole_head", "split_head"])
 @pytest.mark.parametrize("B,Hq,Hkv,T,bits", CASES)
-def test_decode_from_tail_state(B, Hq, Hkv, T, bits):
+def test_decode_from_tail_state(B, Hq, Hkv, T, bits, split):
     case = make_case(300 + T, B, Hq, Hkv, T, bits, random_params=(T % 2 == 1))
     dk, dv, tk, tv, ok_, ov_, sk, sv = _prefill(case, T + 1)
     kn, vn = case["k"][:, :, T], case["v"][:, :, T]
@@ -74,11 +75,11 @@ def test_decode_from_tail_state(B, Hq, Hkv, T, bits):
             SMIN, SMAX)
     # tail_keep: same result and same code, tails untouched; the call can be repeated
     for _ in range(2):
-        got = gemv.decode_attn(*args, bits=bits, k_tail=tk, v_tail=tv, tail_keep=True)
+        got = gemv.decode_attn(*args, bits=bits, k_tail=tk, v_tail=tv, tail_keep=True, split_channels=split)
         np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
         assert torch.equal(tk.view(torch.int32), tk0.view(torch.int32)) and torch.equal(tv.view(torch.int32), tv0.view(torch.int32))
         assert np.array_equal(dk.cpu().numpy(), ok_) and np.array_equal(dv.cpu().numpy(), ov_)
-    got = gemv.decode_attn(*args, bits=bits, k_tail=tk, v_tail=tv)          # contracted replay by default
+    got = gemv.decode_attn(*args, bits=bits, k_tail=tk, v_tail=tv, split_channels=split)   # contracted replay by default
     _status_ok()
     assert got.shape == (B, Hq, 128) and got.dtype == torch.float16
     np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
@@ -86,7 +87,7 @@ def test_decode_from_tail_state(B, Hq, Hkv, T, bits):
     assert _bits_equal(tk, _oracle_tail(sk)) and _bits_equal(tv, _oracle_tail(sv))            # advanced canonically
 
 
-@pytest.mark.parametrize("variant", ["dense", "dense_exact", "varlen", "ckpt", "static"])
+@pytest.mark.parametrize("variant", ["dense", "dense_whole_head", "dense_exact", "varlen", "ckpt", "static"])
 @pytest.mark.parametrize("bits", [4, 2])
 def test_generation_chain_from_tail_state(variant, bits):
     """Prefill, then 40 decode steps that carry the tails; caches and tails stay bit-identical to the oracle's,
@@ -117,8 +118,10 @@ def test_generation_chain_from_tail_state(variant, bits):
         elif variant == "static":
             got = gemv.decode_attn_static(*args, T, 0.1, SMIN, SMAX, bits=bits, k_tail=tk, v_tail=tv, out=out, **kw)
         else:
+            # "dense": the library picks the layout (these few streams: heads split over two warp pairs)
             got = gemv.decode_attn(*args, T, 0.1, SMIN, SMAX, bits=bits, k_tail=tk, v_tail=tv,
-                                   fast=False if variant == "dense_exact" else None, **kw)
+                                   fast=False if variant == "dense_exact" else None,
+                                   split_channels=False if variant == "dense_whole_head" else None, **kw)
         np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     _status_ok()
     assert np.array_equal(dk.cpu().numpy(), ok_) and np.array_equal(dv.cpu().numpy(), ov_)
@@ -199,12 +202,17 @@ def test_full_size_from_tail_state(cfg):
     scaling = D ** -0.5
     want = c_oracle.decode_attn(x(case["q"][:, :, 0]), kc, vc, x(case["k"][:, :, T]), x(case["v"][:, :, T]),
                                 np_params(case["kp"]), np_params(case["vp"]), T, scaling, bits, SMIN, SMAX)
-    out = gemv.decode_attn(rep(case["q"]), dk, dv, rep(case["k"][:, :, T:T + 1]), rep(case["v"][:, :, T:T + 1]),
-                           dev(case["kp"]), dev(case["vp"]), T, scaling, SMIN, SMAX, bits=bits, k_tail=tk, v_tail=tv)
-    _status_ok()
-    got = out.float().cpu().numpy().reshape(B // R, R, Hq, D)
-    assert np.array_equal(got, np.broadcast_to(got[0], got.shape))
-    np.testing.assert_allclose(got[0], want, rtol=RTOL, atol=ATOL)
+    args = (rep(case["q"]), dk, dv, rep(case["k"][:, :, T:T + 1]), rep(case["v"][:, :, T:T + 1]), dev(case["kp"]),
+            dev(case["vp"]), T, scaling, SMIN, SMAX)
+    # the other layout of the heads over warps first (tails kept), then the one the library picks for this size
+    auto_split = B * Hkv <= 160
+    for kw in (dict(split_channels=not auto_split, tail_keep=True), dict()):
+        out = gemv.decode_attn(*args, bits=bits, k_tail=tk, v_tail=tv, **kw)
+        _status_ok()
+        got = out.float().cpu().numpy().reshape(B // R, R, Hq, D)
+        assert np.array_equal(got, np.broadcast_to(got[0], got.shape))
+        np.testing.assert_allclose(got[0], want, rtol=RTOL, atol=ATOL)
+        assert np.array_equal(dk[:R].cpu().numpy(), kc) and np.array_equal(dv[-R:].cpu().numpy(), vc)
     assert np.array_equal(dk[:R].cpu().numpy(), kc) and np.array_equal(dv[-R:].cpu().numpy(), vc)
     assert torch.equal(dk[:R], dk[-R:]) and torch.equal(dv[:R], dv[-R:])
     assert _bits_equal(tk[:R], tk_want) and _bits_equal(tv[-R:], tv_want)

@@ -51,7 +51,7 @@ def test_static_scratch_entry_point_matches_caller_scratch_entry_point(bits, Hq,
         torch.cuda.synchronize()
         assert got is out_b
         np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), rtol=RTOL,
-                                   atol=ATOL * max(1.0, float(want.abs().max())))
+                                   atol=ATOL)
         assert torch.equal(a["k"], b["k"]) and torch.equal(a["v"], b["v"])                # same appended codes
         assert torch.equal(a["kck"], b["kck"]) and torch.equal(a["vck"], b["vck"])        # same checkpoints
     assert gemv.device_status() == 0
