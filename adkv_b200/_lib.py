@@ -40,6 +40,8 @@ SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "adkv_encode_kv_flags": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_uint, c_void_p],
     "adkv_append_kv_flags": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_uint, c_void_p],
+    "adkv_encode_kv_layers": [c_void_p, c_int] + [c_int] * 7 + [c_float, c_float, c_void_p],
+    "adkv_append_kv_layers": [c_void_p, c_int] + [c_int] * 6 + [c_float, c_float, c_void_p],
     "adkv_encode_kv_ckpt": [c_void_p] * 10 + [c_int] * 9 + [c_float, c_float, c_void_p],
     "adkv_append_kv_ckpt": [c_void_p] * 10 + [c_int] * 8 + [c_float, c_float, c_void_p],
     "adkv_decode_attn_ckpt_scratch_bytes": [c_int, c_int, c_int, c_int, c_int],
@@ -68,6 +70,12 @@ class Params(ctypes.Structure):
     """``adkv_params``: five fp16 ``[Hkv, D]`` device pointers."""
     _fields_ = [("zp_init", c_void_p), ("scale_init", c_void_p), ("alpha", c_void_p),
                 ("beta", c_void_p), ("target", c_void_p)]
+
+
+class LayerKV(ctypes.Structure):
+    """``adkv_layer_kv``: K and V of one layer for the layered calls."""
+    _fields_ = [("k_cache", c_void_p), ("k", c_void_p), ("kp", Params), ("k_tail", c_void_p),
+                ("v_cache", c_void_p), ("v", c_void_p), ("vp", Params), ("v_tail", c_void_p)]
 
 
 _lib = None

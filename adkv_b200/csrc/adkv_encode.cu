@@ -2,6 +2,9 @@
 // and the reference interface each one replaces.
 #include "adkv_host.h"
 
+#include <algorithm>
+using std::min;
+
 namespace adkv {
 
 // =========================================================================================
@@ -87,8 +90,9 @@ struct CkptSpec {
     int n_ckpt_cap;
     int D;            // head dim (128, 256 or 512); a CTA handles one 128-channel slice of one stream
 };
+constexpr int kEncMaxTensors = 16;   // tensors per launch: K and V of up to 8 layers (the struct is a kernel parameter)
 struct EncBatch {
-    EncTensor t[2];
+    EncTensor t[kEncMaxTensors];
 };
 
 // WIDE = false: head dim 128, all strides are compile-time constants.
@@ -467,6 +471,55 @@ int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void
     b.t[0] = enc_tensor(k_cache, k_new, kp, k_tail);
     b.t[1] = enc_tensor(v_cache, v_new, vp, v_tail);
     return launch_append(b, 2, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream);
+}
+
+int adkv_encode_kv_layers(const adkv_layer_kv *layers, int n_layers, int B, int H, int T, int D, int n_super_cap,
+                          int bits, int t_start, float scale_min, float scale_max, void *stream)
+{
+    if (!layers) return ADKV_E_NULL;
+    if (n_layers < 0 || t_start < 0) return ADKV_E_SHAPE;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, t_start + T)) return rc;
+    for (int l = 0; l < n_layers; ++l) {
+        if (int rc = encode_check(layers[l].k_cache, layers[l].k, &layers[l].kp, layers[l].k_tail, T, t_start)) return rc;
+        if (int rc = encode_check(layers[l].v_cache, layers[l].v, &layers[l].vp, layers[l].v_tail, T, t_start)) return rc;
+    }
+    if (B * H == 0 || T == 0) return 0;
+    for (int l0 = 0; l0 < n_layers; l0 += kEncMaxTensors / 2) {
+        const int n = min(kEncMaxTensors / 2, n_layers - l0);
+        EncBatch b{};
+        for (int l = 0; l < n; ++l) {
+            const adkv_layer_kv &L = layers[l0 + l];
+            b.t[2 * l] = enc_tensor(L.k_cache, L.k, &L.kp, L.k_tail);
+            b.t[2 * l + 1] = enc_tensor(L.v_cache, L.v, &L.vp, L.v_tail);
+        }
+        if (int rc = launch_encode(b, 2 * n, B, H, T, D, n_super_cap, bits, t_start, scale_min, scale_max, stream)) return rc;
+    }
+    return 0;
+}
+
+int adkv_append_kv_layers(const adkv_layer_kv *layers, int n_layers, int B, int H, int T, int D, int n_super_cap,
+                          int bits, float scale_min, float scale_max, void *stream)
+{
+    if (!layers) return ADKV_E_NULL;
+    if (n_layers < 0) return ADKV_E_SHAPE;
+    if (int rc = check_common(B, H, H, T, D, n_super_cap, bits, T + 1)) return rc;
+    for (int l = 0; l < n_layers; ++l) {
+        const adkv_layer_kv &L = layers[l];
+        if (!L.k_cache || !L.k || !L.k_tail || !params_ok(&L.kp) || !L.v_cache || !L.v || !L.v_tail || !params_ok(&L.vp))
+            return ADKV_E_NULL;
+    }
+    if (B * H == 0) return 0;
+    for (int l0 = 0; l0 < n_layers; l0 += kEncMaxTensors / 2) {
+        const int n = min(kEncMaxTensors / 2, n_layers - l0);
+        EncBatch b{};
+        for (int l = 0; l < n; ++l) {
+            const adkv_layer_kv &L = layers[l0 + l];
+            b.t[2 * l] = enc_tensor(L.k_cache, L.k, &L.kp, L.k_tail);
+            b.t[2 * l + 1] = enc_tensor(L.v_cache, L.v, &L.vp, L.v_tail);
+        }
+        if (int rc = launch_append(b, 2 * n, B, H, T, D, n_super_cap, bits, scale_min, scale_max, stream)) return rc;
+    }
+    return 0;
 }
 
 int adkv_encode_kv_ckpt(void *k_cache, const void *k, const adkv_params *kp, void *k_tail, void *k_ckpt,

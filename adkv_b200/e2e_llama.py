@@ -85,6 +85,7 @@ class ADKVLlama:
         self.fast = self.keeps_tails if fast is None else fast
         self.peers = peers
         self.split_channels = split_channels      # layout of a head over warps in the eager fused step (None: automatic)
+        self._marks = None                        # event recorder of profile_decode_step
         self.hq, self.hkv, self.ffn = shape.n_heads // world, shape.n_kv_heads // world, shape.ffn // world
         D, dm = shape.head_dim, shape.d_model
         g = torch.Generator(device=self.dev)
@@ -141,11 +142,19 @@ class ADKVLlama:
                                        dtype=torch.uint8, device=self.dev)
 
     # ------------------------------------------------------------------ helpers
+    def _mark(self, name: str) -> None:
+        """While profile_decode_step runs: a CUDA event that closes the segment `name`."""
+        if self._marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
     def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
             if self.peers is not None:      # shards of one process: summed by step_together
                 raise RuntimeError("shards that share a process are stepped with step_together()")
             dist.all_reduce(x)
+        self._mark("all_reduce")
         return x
 
     def _tails(self, L, b0=None, b1=None):
@@ -203,6 +212,7 @@ class ADKVLlama:
         q, k, v = self._qkv(L, h, 1)
         q, k = _apply_rope(q, cos, sin).contiguous(), _apply_rope(k, cos, sin).contiguous()
         v = v.contiguous()
+        self._mark("norm_qkv_rope")
         smin, smax = synth.SCALE_MIN, synth.SCALE_MAX
         if seq_lens is not None:
             att = gemv.decode_attn_varlen(q, L["kc"], L["vc"], k, v, L["kp"], L["vp"], seq_lens, self.scaling, smin, smax,
@@ -217,16 +227,45 @@ class ADKVLlama:
             w = torch.softmax(logits.float() * self.scaling, dim=-1).to(torch.float16)
             att = gemv.forward_ov(w, L["vc"], v, *L["vp"], smin, smax, bits=self.bits, fast=self.fast,
                                   half_state=self.half_state)
-        return att.reshape(self.B, 1, -1) @ L["wo"].T
+        self._mark("attention_kernels")
+        out = att.reshape(self.B, 1, -1) @ L["wo"].T
+        self._mark("o_proj")
+        return out
 
     def _mlp_partial(self, L, x):
         gu = _rms_norm(x, L["norm2"], self.s.norm_eps) @ L["w_gate_up"].T
-        return (F.silu(gu[..., :self.ffn]) * gu[..., self.ffn:]) @ L["w_down"].T
+        out = (F.silu(gu[..., :self.ffn]) * gu[..., self.ffn:]) @ L["w_down"].T
+        self._mark("norm_mlp")
+        return out
 
     def _head(self, x):
         last = _rms_norm(x[:, 0], self.final_norm, self.s.norm_eps)
         self.last_logits = last @ self.lm_head.T
-        return self.last_logits.argmax(-1)
+        tok = self.last_logits.argmax(-1)
+        self._mark("final_norm_lm_head")
+        return tok
+
+    @torch.no_grad()
+    def profile_decode_step(self, ids: torch.Tensor, steps: int = 4) -> tuple[torch.Tensor, dict]:
+        """Run `steps` eager decode steps with a CUDA event after every segment of the step; returns the last
+        tokens and the milliseconds per step spent in each kind of segment (device time between events, so host
+        launch gaps are charged to the segment they precede; the residual additions ride with the all-reduce)."""
+        totals: dict = {}
+        tok = ids
+        for _ in range(steps):
+            self._marks = []
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
+            tok = self.decode(tok)
+            marks, self._marks = self._marks, None
+            torch.cuda.synchronize(self.dev)
+            prev = start
+            for name, ev in marks:
+                totals[name] = totals.get(name, 0.0) + prev.elapsed_time(ev)
+                prev = ev
+        per_step = {k: v / steps for k, v in totals.items()}
+        per_step["step_total"] = sum(per_step.values())
+        return tok, per_step
 
     # ------------------------------------------------------------------ decode, replayable
     @torch.no_grad()
@@ -332,7 +371,7 @@ def prefill_together(shards: list, ids: torch.Tensor) -> torch.Tensor:
 
 
 def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fused: bool = True, fast: bool | None = None,
-        ckpt_interval: int = 0, seed: int = 0, graph: bool = False, half_state: bool = False) -> dict:
+        ckpt_interval: int = 0, seed: int = 0, graph: bool = False, half_state: bool = False, breakdown: int = 0) -> dict:
     """Prefill a random prompt, generate `gen` tokens greedily; timings with CUDA events, max over ranks."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -341,7 +380,7 @@ def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fus
     dev = torch.device("cuda", local)
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
-    model = ADKVLlama(shape, batch, prompt + gen, bits=bits, device=dev, rank=rank, world=world, seed=seed,
+    model = ADKVLlama(shape, batch, prompt + gen + breakdown, bits=bits, device=dev, rank=rank, world=world, seed=seed,
                       fused=fused, fast=fast, ckpt_interval=ckpt_interval, half_state=half_state)
     g = torch.Generator(device=dev)
     g.manual_seed(seed + 99)
@@ -368,6 +407,10 @@ def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fus
             out.append(tok)
     ev[2].record()
     torch.cuda.synchronize(dev)
+    step_breakdown = None
+    if breakdown and model.T + breakdown <= prompt + gen + breakdown:
+        # extra eager steps after the timed region (the caches were sized for them)
+        _, step_breakdown = model.profile_decode_step(tok, breakdown)
     t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -378,7 +421,7 @@ def run(shape: LlamaShape, batch: int, prompt: int, gen: int, bits: int = 4, fus
                 decode_tokens_per_s=batch * gen / (decode_ms * 1e-3), ms_per_decode_step=decode_ms / gen,
                 prefill_tokens_per_s=batch * prompt / (prefill_ms * 1e-3), device_status=status,
                 token_checksum=int(toks.sum().item()), tokens=toks, fast=bool(model.fast),
-                tail_states=model.keeps_tails)
+                tail_states=model.keeps_tails, eager_step_breakdown_ms=step_breakdown)
 
 
 def main():
@@ -395,11 +438,14 @@ def main():
                     help="the fp16-state arithmetic of the reference's CUDA kernels instead of the fp32 recurrence")
     ap.add_argument("--ckpt-interval", type=int, default=0)
     ap.add_argument("--graph", action="store_true", help="replay the decode step from a CUDA graph (device-side lengths)")
+    ap.add_argument("--breakdown", type=int, default=0,
+                    help="after the timed run, this many extra eager steps with CUDA events around every segment "
+                         "(attention kernels, projections, MLP, all-reduces)")
     a = ap.parse_args()
     shape = LlamaShape(n_layers=a.layers)
     r = run(shape, a.batch, a.prompt, a.gen, bits=a.bits, fused=not a.unfused,
             fast=True if a.fast else (False if a.exact else None),
-            ckpt_interval=a.ckpt_interval, graph=a.graph, half_state=a.half_state)
+            ckpt_interval=a.ckpt_interval, graph=a.graph, half_state=a.half_state, breakdown=a.breakdown)
     if r["rank"] == 0:
         r.pop("tokens")
         r.update(metric="e2e_decode_tokens_per_s", config=dict(model="random-init Llama-2-7B architecture", batch=a.batch,

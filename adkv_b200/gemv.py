@@ -19,6 +19,7 @@ Arithmetic is the reference's fp32 torch/Triton recurrence
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 
 import torch
@@ -27,7 +28,7 @@ from . import _lib
 
 __all__ = ["encode_kv", "forward_qk", "forward_ov", "decode_attn", "append_kv", "encode_kv_pair",
            "append_kv_pair", "n_super_for", "alloc_ckpt", "ckpt_capacity", "decode_scratch_bytes",
-           "decode_attn_varlen", "decode_attn_static"]
+           "decode_attn_varlen", "decode_attn_static", "encode_kv_layers", "append_kv_layers", "LayerSet"]
 
 
 def n_super_for(tokens: int, bits: int = 4) -> int:
@@ -68,28 +69,35 @@ def _require(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
-# Parameter tensors are the same five objects call after call (one set per layer and tensor): the checked
-# ``adkv_params`` struct is remembered per set.  An entry holds the tensors, so their ids cannot be reused while it
-# is cached; a tensor whose storage was swapped since is caught by comparing the pointers.
-_PARAM_CACHE: dict = {}
-_PARAM_CACHE_MAX = 1024
+# Parameter tensors are the same five buffers call after call (one set per layer and tensor): the checked
+# ``adkv_params`` struct is remembered per set of device addresses.  An entry holds five integers and a small ctypes
+# struct, never a tensor, so nothing is kept alive; a buffer that is freed and whose address is later reused by another
+# tensor of the same dtype and size yields the very same struct, which is then just as right.  Least recently used
+# entries are dropped one at a time.
+_PARAM_CACHE: "collections.OrderedDict" = collections.OrderedDict()
+_PARAM_CACHE_MAX = 512
 
 
 def _params(names, tensors, H, D, device):
-    key = tuple(map(id, tensors))
-    hit = _PARAM_CACHE.get(key)
-    if hit is not None and hit[2] == (H, D, device) and hit[3] == tuple(t.data_ptr() for t in tensors):
-        return hit[0], hit[1]
+    """(adkv_params struct, tensors that must outlive the call) for five [H, D] float16 parameter tensors."""
+    if all(t.is_contiguous() for t in tensors):
+        key = (H, D, device, tuple((t.data_ptr(), t.dtype, t.numel(), t.device) for t in tensors))
+        hit = _PARAM_CACHE.get(key)
+        if hit is not None:
+            _PARAM_CACHE.move_to_end(key)
+            return hit, tensors
+    else:
+        key = None
     for n, t in zip(names, tensors):
         _require(t.dtype == torch.float16, f"{n} must be float16")
         _require(t.is_cuda and t.device == device, f"{n} must be on the cache's CUDA device")
         _require(t.numel() == H * D, f"{n} must have {H} x {D} elements")
     keep = [t.contiguous() for t in tensors]
     p = _lib.Params(*[t.data_ptr() for t in keep])
-    if len(_PARAM_CACHE) >= _PARAM_CACHE_MAX:
-        _PARAM_CACHE.clear()
-    # `tensors` are kept too: an id stays taken for as long as its object lives
-    _PARAM_CACHE[key] = (p, keep, (H, D, device), tuple(t.data_ptr() for t in tensors), tuple(tensors))
+    if key is not None:
+        _PARAM_CACHE[key] = p
+        if len(_PARAM_CACHE) > _PARAM_CACHE_MAX:
+            _PARAM_CACHE.popitem(last=False)
     return p, keep
 
 
@@ -253,6 +261,85 @@ def append_kv_pair(k_cache, k_new, k_params, k_tail, v_cache, v_new, v_params, v
                                             n_super_cap, bits, scale_min, scale_max, _stream(k_cache))
     _lib.check(rc, "append_kv_pair")
     return k_cache, v_cache
+
+
+class LayerSet:
+    """The packed caches, parameters and tail states of several layers, bound once for the layered calls.
+
+    ``layers``: one tuple ``(k_cache, k_params, k_tail, v_cache, v_params, v_tail)`` per layer; all layers share
+    shapes.  Building the descriptor array (argument checks, pointer extraction) is what a per-layer call pays
+    on every step; a ``LayerSet`` pays it once, and :func:`encode_kv_layers` / :func:`append_kv_layers` then only
+    fill in the pointers of the new tokens.  The caches and tails must stay the tensors they were bound with."""
+
+    def __init__(self, layers, bits: int = 4):
+        layers = list(layers)
+        _require(len(layers) > 0, "a LayerSet needs at least one layer")
+        kc0 = layers[0][0]
+        self.B, self.H, self.n_super_cap, self.D = _cache_dims(kc0, "k_cache")
+        self.bits, self.device, self.n = bits, kc0.device, len(layers)
+        self._keep = []
+        self.desc = (_lib.LayerKV * self.n)()
+        names = ("zp", "sc", "alpha", "beta", "target")
+        for i, (kc, kps, kt, vc, vps, vt) in enumerate(layers):
+            for c in (kc, vc):
+                _require(tuple(c.shape) == tuple(kc0.shape) and c.dtype == torch.uint8 and c.is_cuda and c.is_contiguous()
+                         and c.device == self.device, "every cache of a LayerSet must be a contiguous uint8 tensor of one shape")
+            kp, keep_k = _params(names, tuple(kps), self.H, self.D, self.device)
+            vp, keep_v = _params(names, tuple(vps), self.H, self.D, self.device)
+            d = self.desc[i]
+            d.k_cache, d.v_cache = kc.data_ptr(), vc.data_ptr()
+            d.kp, d.vp = kp, vp
+            d.k_tail, d.v_tail = _tail_ptr(kt, self.B, self.H, self.D), _tail_ptr(vt, self.B, self.H, self.D)
+            self._keep.append((kc, vc, kt, vt, keep_k, keep_v))
+
+    def _bind_new(self, k_new, v_new, tokens_dims):
+        """Point the descriptors at the new tokens: two lists of per-layer tensors, or two stacked tensors
+        ``[n_layers, B, H, ...]``."""
+        _require(len(k_new) == self.n and len(v_new) == self.n, "one K and one V tensor per layer")
+        keep = []
+        for i in range(self.n):
+            for x in (k_new[i], v_new[i]):
+                _require(x.dtype == torch.float16 and x.is_cuda, "new tokens must be float16 CUDA tensors")
+            xk, xv = k_new[i].contiguous(), v_new[i].contiguous()
+            _require(xk.numel() == tokens_dims and xv.numel() == tokens_dims, "new tokens have the wrong shape")
+            self.desc[i].k, self.desc[i].v = xk.data_ptr(), xv.data_ptr()
+            keep.append((xk, xv))
+        return keep
+
+
+def encode_kv_layers(layer_set: LayerSet, k_new, v_new, scale_min, scale_max, *, t_start: int = 0):
+    """:func:`encode_kv_pair` for every layer of ``layer_set`` in as few launches as possible (K and V of 8 layers
+    each).  ``k_new`` / ``v_new``: per layer ``[B, nh, T, DIM]`` float16 (lists, or tensors stacked along a leading
+    layer axis).  For callers that hold the fp16 K/V of many layers at once."""
+    ls = layer_set
+    T = k_new[0].shape[2]
+    need = n_super_for(t_start + T, ls.bits)
+    _require(need <= ls.n_super_cap, f"kv_cache capacity too small: need {need} supergroups, have {ls.n_super_cap}")
+    keep = ls._bind_new(k_new, v_new, ls.B * ls.H * T * ls.D)
+    with _on_device(ls.device):
+        rc = _lib.load().adkv_encode_kv_layers(ctypes.addressof(ls.desc), ls.n, ls.B, ls.H, T, ls.D, ls.n_super_cap,
+                                               ls.bits, t_start, scale_min, scale_max,
+                                               ctypes.c_void_p(_raw_stream(ls.device.index)) if _raw_stream else
+                                               ctypes.c_void_p(torch.cuda.current_stream(ls.device).cuda_stream))
+    _lib.check(rc, "encode_kv_layers")
+    del keep
+
+
+def append_kv_layers(layer_set: LayerSet, k_new, v_new, T: int, scale_min, scale_max):
+    """:func:`append_kv_pair` for every layer of ``layer_set``: token ``T`` of every layer is quantised from that
+    layer's tail states, which advance.  ``k_new`` / ``v_new``: per layer ``[B, nh, 1, DIM]`` float16 (lists or a
+    tensor stacked along a leading layer axis, e.g. one ``[n_layers, B, nh, DIM]`` buffer the layers wrote into)."""
+    ls = layer_set
+    _require(T >= 0 and T // (32 // ls.bits) < ls.n_super_cap, f"cache has no free supergroup to append token {T}")
+    _require(all(ls.desc[i].k_tail and ls.desc[i].v_tail for i in range(ls.n)), "append needs the tail states")
+    keep = ls._bind_new(k_new, v_new, ls.B * ls.H * ls.D)
+    with _on_device(ls.device):
+        rc = _lib.load().adkv_append_kv_layers(ctypes.addressof(ls.desc), ls.n, ls.B, ls.H, T, ls.D, ls.n_super_cap,
+                                               ls.bits, scale_min, scale_max,
+                                               ctypes.c_void_p(_raw_stream(ls.device.index)) if _raw_stream else
+                                               ctypes.c_void_p(torch.cuda.current_stream(ls.device).cuda_stream))
+    _lib.check(rc, "append_kv_layers")
+    del keep
 
 
 def append_kv(cache, x_new, zp, sc, alpha, beta, target, tail, T: int, scale_min, scale_max, *, bits: int = 4,

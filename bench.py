@@ -68,10 +68,10 @@ UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel (bytes), from an ncu capture;
 # None where no capture exists for the workload.
 NCU_TRAFFIC_BYTES = {
-    # 273.3 MB measured on a batch-16 capture of the same kernel; streams are independent, so traffic scales
-    # with the batch: x8 for batch 128
-    "config2_llama2_7b_b128_t4096_4bit": 8 * 273_308_672,
-    "profile_b16_t4096_4bit": 273_308_672,
+    # 274.8 MB measured on a batch-16 capture of the same kernel (tail path); streams are independent, so traffic
+    # scales with the batch: x8 for batch 128
+    "config2_llama2_7b_b128_t4096_4bit": 8 * 274_810_624,
+    "profile_b16_t4096_4bit": 274_810_624,
 }
 
 
@@ -283,6 +283,13 @@ def pick_torch_sample(w, step_budget_s: float):
     return 1, 1, int(max(32, min(T, step_budget_s / (per_tok_fixed + per_tok_head))))
 
 
+def use_all_host_threads(torch) -> int:
+    """Let torch use every core this process may run on (launchers export OMP_NUM_THREADS=1 for every rank)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def timed_cpu(fn, repeats: int = 1):
     best, res = float("inf"), None
     for _ in range(repeats):
@@ -324,6 +331,7 @@ def run_reference(args, w, name):
     from oracle import c_oracle, ref_torch
     w_rank = rank_workload(w, world, 0, args.scaling)
     budget = min(2.0, max(0.05, 120.0 / (args.steps + args.warmup)))
+    use_all_host_threads(torch)
     if ref_torch.available():
         smp = torch_reference_sample(w, *pick_torch_sample(w, budget))
         step = lambda: torch_reference_step(smp)
@@ -650,7 +658,22 @@ def encode_ms(w, torch, device, steps):
                             synth.SCALE_MAX, bits=bits)
     a1.record()
     torch.cuda.synchronize(device)
-    return ms, a0.elapsed_time(a1) * 1e3 / A
+    append_us = a0.elapsed_time(a1) * 1e3 / A
+    # the layered calls: K and V of 8 layers per launch (the same input tensors stand for every layer; each layer
+    # has its own caches and tails, so the bytes written and the chains run are those of 8 layers)
+    NL = 8
+    caches = [(torch.zeros_like(kc), torch.empty_like(tk), torch.zeros_like(vc), torch.empty_like(tv)) for _ in range(NL)]
+    ls = gemv.LayerSet([(c[0], kp, c[1], c[2], vp, c[3]) for c in caches], bits=bits)
+    ms_layers = time_cuda(lambda: gemv.encode_kv_layers(ls, [k] * NL, [v] * NL, synth.SCALE_MIN, synth.SCALE_MAX),
+                          torch, device, max(2, steps // 2), warmup=2) / NL
+    kn_l = [kn[:, :, 0:1].contiguous()] * NL
+    vn_l = [vn[:, :, 0:1].contiguous()] * NL
+    a0.record()
+    for i in range(A):
+        gemv.append_kv_layers(ls, kn_l, vn_l, T + i, synth.SCALE_MIN, synth.SCALE_MAX)
+    a1.record()
+    torch.cuda.synchronize(device)
+    return ms, append_us, ms_layers, a0.elapsed_time(a1) * 1e3 / A / NL
 
 
 def other_workload_figures(torch, device, peak):
@@ -658,10 +681,13 @@ def other_workload_figures(torch, device, peak):
     res = {}
     for name in ("config3_prefill_b16_t8192_4bit", "config3_prefill_b16_t8192_2bit"):
         w = WORKLOADS[name]
-        ms, app_us = encode_ms(w, torch, device, 5)
-        gbs = algorithmic_bytes(w) / (ms * 1e-3) / 1e9
+        ms, app_us, ms_l, app_us_l = encode_ms(w, torch, device, 5)
+        gbs, gbs_l = algorithmic_bytes(w) / (ms * 1e-3) / 1e9, algorithmic_bytes(w) / (ms_l * 1e-3) / 1e9
         res[name] = {"ms_per_layer_kv": ms, "value": gbs, "unit": UNIT, "frac_of_measured_peak": gbs / peak,
-                     "append_us_per_token_kv": app_us, "layers_in_the_configuration": 32}
+                     "append_us_per_token_kv": app_us, "layers_in_the_configuration": 32,
+                     "eight_layers_per_launch": {"ms_per_layer_kv": ms_l, "value": gbs_l, "unit": UNIT,
+                                                 "frac_of_measured_peak": gbs_l / peak,
+                                                 "append_us_per_layer_token_kv": app_us_l}}
         torch.cuda.empty_cache()
     name = "config5_llama3_8b_gqa_b32_t32768_2bit"
     w = WORKLOADS[name]
@@ -869,6 +895,7 @@ def run_ours(args, w, name):
             from oracle import ref_torch
             if ref_torch.available():
                 # the reference's own torch path on the host cores: one sequence of the workload, best of 2
+                use_all_host_threads(torch)
                 smp = torch_reference_sample(w, *pick_torch_sample(w, 6.0))
                 secs, want = timed_cpu(lambda: torch_reference_step(smp), repeats=2)
                 res["cpu_baseline"] = {"value": torch_sample_bytes(w, smp) / secs / 1e9, "unit": UNIT,

@@ -123,6 +123,24 @@ int adkv_append_kv(void *k_cache, const void *k_new, const adkv_params *kp, void
                    int B, int H, int T, int D, int n_super_cap, int bits,
                    float scale_min, float scale_max, void *stream);
 
+/* K and V of one layer for the layered calls below.  `k` / `v`: the fp16 tokens to quantise ([B, H, T, D] for prefill,
+ * [B, H, D] for an append); tails as in adkv_encode / adkv_append (required for an append). */
+typedef struct adkv_layer_kv {
+    void *k_cache; const void *k; adkv_params kp; void *k_tail;
+    void *v_cache; const void *v; adkv_params vp; void *v_tail;
+} adkv_layer_kv;
+
+/* adkv_encode_kv / adkv_append_kv for several layers at once: `layers` is a HOST array of n_layers descriptors, all
+ * layers share shapes, bits and clamp bounds, and K and V of up to 8 layers go into one launch.  No counterpart in the
+ * reference, which quantises one tensor per call (src/adkv/hf/llama_adkv.py:144-153).  For callers that hold the
+ * fp16 K/V of many layers at once -- converting an existing fp16 cache, or appending the token of a step to every
+ * layer's cache after the layers have run: the quantiser is bound by its token-sequential chain and by launch
+ * overhead, not by bandwidth, so more independent streams per launch and fewer launches are what it needs. */
+int adkv_encode_kv_layers(const adkv_layer_kv *layers, int n_layers, int B, int H, int T, int D, int n_super_cap,
+                          int bits, int t_start, float scale_min, float scale_max, void *stream);
+int adkv_append_kv_layers(const adkv_layer_kv *layers, int n_layers, int B, int H, int T, int D, int n_super_cap,
+                          int bits, float scale_min, float scale_max, void *stream);
+
 /* The general forms of prefill and append: adkv_encode_kv(_ckpt) / adkv_append_kv(_ckpt) with a `flags` argument
  * (ADKV_FLAG_HALF_STATE selects the arithmetic of the reference's CUDA kernels; with 0 they are the calls above and
  * below).  v_cache == NULL: one tensor only (the K arguments; no checkpoints then).  interval == 0: no state

@@ -498,3 +498,36 @@ def test_argument_errors_raise_runtime_error():
                         torch.zeros(1, H, 1, 64, dtype=torch.float16, device="cuda"),
                         *[t[:, :64].contiguous() for t in p], 3, SMIN, SMAX)
     assert gemv.forward_qk(q, cache, q, *p, 15, SMIN, SMAX).shape == (1, H, 16)     # last legal slot
+
+
+@pytest.mark.parametrize("bits,n_layers", [(4, 3), (2, 11)])
+def test_layered_encode_and_append_equal_per_layer_calls(bits, n_layers):
+    """adkv_encode_kv_layers / adkv_append_kv_layers (K and V of up to 8 layers per launch, 11 layers = two
+    launches): caches and tails bit-identical to one call per layer, which the tests above hold to the oracle."""
+    B, H, D, T, A = 2, 2, 128, 45, 5
+    ns = orc.n_super_for(T + A, bits)
+    mk = lambda: torch.zeros(orc.cache_shape(B, H, ns, D), dtype=torch.uint8, device="cuda")
+    tail = lambda: torch.zeros(B, H, 2, D, dtype=torch.float32, device="cuda")
+    ks = [dev(synth.gen_kv(50 + 2 * l, B, H, T + A, D)) for l in range(n_layers)]
+    vs = [dev(synth.gen_kv(51 + 2 * l, B, H, T + A, D)) for l in range(n_layers)]
+    kps = [dev(synth.gen_params(70 + l, H, D, bits)) for l in range(n_layers)]
+    vps = [dev(synth.gen_params(90 + l, H, D, bits)) for l in range(n_layers)]
+    one = [(mk(), tail(), mk(), tail()) for _ in range(n_layers)]
+    many = [(mk(), tail(), mk(), tail()) for _ in range(n_layers)]
+    for l, (kc, kt, vc, vt) in enumerate(one):
+        gemv.encode_kv_pair(kc, ks[l][:, :, :T], kps[l], vc, vs[l][:, :, :T], vps[l], SMIN, SMAX, bits=bits, k_tail=kt, v_tail=vt)
+        for t in range(T, T + A):
+            gemv.append_kv_pair(kc, ks[l][:, :, t:t + 1], kps[l], kt, vc, vs[l][:, :, t:t + 1], vps[l], vt, t, SMIN, SMAX, bits=bits)
+    ls = gemv.LayerSet([(kc, kps[l], kt, vc, vps[l], vt) for l, (kc, kt, vc, vt) in enumerate(many)], bits=bits)
+    gemv.encode_kv_layers(ls, [k[:, :, :T] for k in ks], [v[:, :, :T] for v in vs], SMIN, SMAX)
+    for t in range(T, T + A):
+        # the new tokens of all layers as one stacked buffer, the way a model step would leave them
+        kn = torch.stack([k[:, :, t] for k in ks])
+        vn = torch.stack([v[:, :, t] for v in vs])
+        gemv.append_kv_layers(ls, kn, vn, t, SMIN, SMAX)
+    _status_ok()
+    for (kc1, kt1, vc1, vt1), (kc2, kt2, vc2, vt2) in zip(one, many):
+        assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+        assert torch.equal(kt1.view(torch.int32), kt2.view(torch.int32)) and torch.equal(vt1.view(torch.int32), vt2.view(torch.int32))
+    with pytest.raises(RuntimeError, match="no free supergroup"):
+        gemv.append_kv_layers(ls, kn, vn, ns * (32 // bits), SMIN, SMAX)

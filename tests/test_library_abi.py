@@ -96,3 +96,33 @@ def test_argument_errors_of_the_flagged_entry_points():
         assert app(16, 16, pp, None, None, None, None, None, 1, 1, 3, 128, 1, 4) == -1         # no tail state
         assert app(16, 16, pp, 16, None, None, None, None, 1, 1, 8, 128, 1, 4) == -5
     assert _lib.strerror(-10).startswith("adkv:")
+
+
+def test_parameter_struct_cache_is_bounded_and_pins_nothing(monkeypatch):
+    """The per-layer parameter structs are cached by device address in an LRU that holds no tensors."""
+    import gc
+    import weakref
+
+    class FakeParam:
+        """Stands in for a CUDA tensor: the cache only looks at address, dtype, size, device and contiguity."""
+        def __init__(self, addr):
+            self.addr, self.dtype, self.is_cuda, self.device = addr, torch.float16, True, "cuda:0"
+        def data_ptr(self): return self.addr
+        def numel(self): return 2 * 128
+        def is_contiguous(self): return True
+        def contiguous(self): return self
+
+    monkeypatch.setattr(gemv, "_PARAM_CACHE_MAX", 4)
+    gemv._PARAM_CACHE.clear()
+    sets = [tuple(FakeParam(1000 * (i + 1) + 16 * j) for j in range(5)) for i in range(7)]
+    refs = [weakref.ref(s[0]) for s in sets]
+    for s in sets:
+        p, keep = gemv._params(("a", "b", "c", "d", "e"), s, 2, 128, "cuda:0")
+        assert p.zp_init == s[0].addr and p.target == s[4].addr
+    assert len(gemv._PARAM_CACHE) == 4                              # oldest entries dropped one at a time
+    first = gemv._params(("a",) * 5, sets[6], 2, 128, "cuda:0")[0]
+    assert first is gemv._params(("a",) * 5, sets[6], 2, 128, "cuda:0")[0]   # a hit returns the cached struct
+    del sets, s, keep
+    gc.collect()
+    assert all(r() is None for r in refs)                           # nothing in the cache kept the tensors alive
+    gemv._PARAM_CACHE.clear()
