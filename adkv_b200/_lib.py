@@ -18,6 +18,7 @@ FLAG_HALF_STATE = 2
 FLAG_TAIL_KEEP = 4
 FLAG_SPLIT_CHANNELS = 8
 FLAG_NO_SPLIT_CHANNELS = 16
+FLAG_SELFTEST_MUTE_K = 0x80000000
 ABI_VERSION = 2
 
 

@@ -13,7 +13,10 @@ namespace adkv {
 // (half2 per lane) and per supergroup it writes 256 contiguous bytes (uint2 per lane).  The next
 // word's tokens are fetched while the current word is quantised.
 constexpr int kEncThreads = kD / 2;
-constexpr int kEncStages = 3;   // 32-token (8 KB) tiles of fp16 input in flight per CTA; 24 KB lets 7+ CTAs share an SM,
+#ifndef ADKV_ENC_STAGES
+#define ADKV_ENC_STAGES 3
+#endif
+constexpr int kEncStages = ADKV_ENC_STAGES;   // 32-token (8 KB) tiles of fp16 input in flight per CTA; 24 KB lets 7+ CTAs share an SM,
                                 // so K and V of 512 streams (1024 CTAs) run as a single wave on 148 SMs
 
 // Eight tokens for the two channels of a thread,

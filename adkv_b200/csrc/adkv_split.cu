@@ -51,6 +51,7 @@ struct PartialSrc : SoftmaxSrc<G, 1, HALF_W> {
 struct CkptArgs {
     float *k_ckpt, *v_ckpt;   // [B*Hkv][n_ckpt_cap][2][kD]; entry k = state before token (k+1)*interval
     int interval, n_ckpt_cap;
+    bool mute_k;              // self-test (ADKV_FLAG_SELFTEST_MUTE_K): the K warps do nothing, so every V warp's wait runs out
 };
 
 template <int BITS, int G, int MODE>
@@ -85,6 +86,7 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
     const bool write_ckpt = seg.append && (T + 1) % ck.interval == 0;
     const size_t out_idx = write_ckpt ? stream_ckpt + (T + 1) / ck.interval - 1 : 0;
     if (warp == 0) {
+        if (ck.mute_k) return;
         seg.init = j ? ck.k_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
         seg.ckpt_out = write_ckpt ? ck.k_ckpt + out_idx * 2 * kD : nullptr;
         RingSink<G> sink{&fs, 0, 0};
@@ -187,7 +189,8 @@ int adkv_decode_attn_ckpt(const void *q, void *k_cache, void *v_cache, const voi
                    static_cast<float *>(k_tail), keep};
     const VArgs va{static_cast<uint8_t *>(v_cache), static_cast<const __half *>(v_new), static_cast<__half *>(out),
                    to_ptrs(vp), Hq, Hkv, T, n_super_cap, scale_min, scale_max, D, static_cast<float *>(v_tail), keep};
-    const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap};
+    const CkptArgs ck{static_cast<float *>(k_ckpt), static_cast<float *>(v_ckpt), interval, n_ckpt_cap,
+                      (flags & ADKV_FLAG_SELFTEST_MUTE_K) != 0};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool exact = !(flags & ADKV_FLAG_FAST_REPLAY);
     const int n_seg = T / interval + 1;

@@ -74,6 +74,11 @@ extern "C" {
  * or the other (tests, tuning); with both set, SPLIT wins. */
 #define ADKV_FLAG_SPLIT_CHANNELS 8u
 #define ADKV_FLAG_NO_SPLIT_CHANNELS 16u
+/* Self-test of the failure path of adkv_decode_attn_ckpt (no counterpart in the reference): the K warps return at
+ * once, so every V warp waits for logits that never come.  Each wait gives up after its 1 s limit, the kernels end
+ * normally, adkv_device_status reports 3, nothing is appended, and every element of `out` is NaN -- a segment that
+ * could not be finished marks its partial result instead of leaving whatever the scratch memory held. */
+#define ADKV_FLAG_SELFTEST_MUTE_K 0x80000000u
 
 /* The five per-(kv head, channel) parameter tensors, fp16 [Hkv, D] each
  * (src/adkv/hf/llama_adkv.py:27: zp_init, scale_init, alpha, beta, quant_target). */

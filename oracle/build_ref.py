@@ -41,6 +41,11 @@ STAGED = ("adkv/__init__.py", "adkv/kernel/__init__.py", "adkv/hf/llama_adkv.py"
           "adkv/train/train_model.py")
 
 
+# The reference's kernel module, kept as TEXT for the signature comparison of tests/test_boundary.py.  It is given a
+# name Python cannot import: importing it would JIT-build the reference's extension.
+KERNEL_MODULE_TEXT = os.path.join(OUT_DIR, "reference_kernel_module_gemv.py.txt")
+
+
 def stage_python(ref_root: str) -> str | None:
     """Copy the STAGED files, unchanged, to oracle/_ref/src/.  Returns that folder, or None without a checkout."""
     src = os.path.join(ref_root, "src")
@@ -52,6 +57,7 @@ def stage_python(ref_root: str) -> str | None:
             continue
         os.makedirs(os.path.dirname(b), exist_ok=True)
         shutil.copyfile(a, b)
+    shutil.copyfile(os.path.join(src, "adkv", "kernel", "gemv.py"), KERNEL_MODULE_TEXT)
     return SRC_DIR
 
 

@@ -5,7 +5,7 @@ import torch
 
 from adkv_b200 import gemv, synth
 from oracle import adkv_oracle as orc
-from tests.util import SMAX, SMIN, dev, make_case, np_params
+from tests.util import SMAX, SMIN, dev, make_case, np_params, oracle_prefill
 
 pytestmark = pytest.mark.gpu
 RTOL, ATOL = 2e-3, 2e-3
@@ -88,3 +88,47 @@ def test_checkpointed_append_and_errors():
     small = gemv.alloc_ckpt(B, H, D, 64, S, "cuda")
     with pytest.raises(RuntimeError, match="capacity"):
         gemv.decode_attn(q, kc, vc, q, q, p, p, T + 1, 0.1, SMIN, SMAX, k_ckpt=small, v_ckpt=small.clone(), ckpt_interval=S)
+
+
+def test_segment_that_gives_up_marks_its_result():
+    """Failure path of the checkpointed step, made on purpose without faulting anything: with the K warps muted no
+    logits ever arrive, every V warp's bounded wait runs out (1 s), the kernels end normally and the context stays
+    usable.  The status word names the wait, and the output is NaN everywhere -- not the previous call's result,
+    which the scratch memory still held."""
+    import ctypes
+    import time
+
+    from adkv_b200 import _lib
+    B, H, T, bits, D, iv = 1, 2, 70, 4, 128, 32
+    case = make_case(31, B, H, H, T, bits)
+    kc, vc = oracle_prefill(case)
+    dk, dv = dev(kc), dev(vc)
+    kck, vck = gemv.alloc_ckpt(B, H, D, T + 1, iv, "cuda"), gemv.alloc_ckpt(B, H, D, T + 1, iv, "cuda")
+    gemv.encode_kv_pair(torch.zeros_like(dk), dev(case["k"][:, :, :T]), dev(case["kp"]), torch.zeros_like(dv),
+                        dev(case["v"][:, :, :T]), dev(case["vp"]), SMIN, SMAX, bits=bits, k_ckpt=kck, v_ckpt=vck,
+                        ckpt_interval=iv)
+    q, kn, vn = dev(case["q"]), dev(case["k"][:, :, T:T + 1]), dev(case["v"][:, :, T:T + 1])
+    kp, vp = dev(case["kp"]), dev(case["vp"])
+    scratch = torch.empty(gemv.decode_scratch_bytes(B, H, H, T, iv), dtype=torch.uint8, device="cuda")
+    good = gemv.decode_attn(q, dk, dv, kn, vn, kp, vp, T, 0.1, SMIN, SMAX, bits=bits, k_ckpt=kck, v_ckpt=vck,
+                            ckpt_interval=iv, scratch=scratch)
+    assert torch.isfinite(good).all() and gemv.device_status() == 0
+    before_k = dk.clone()
+    out = torch.zeros_like(good)
+    P = lambda ps: _lib.Params(*[t.data_ptr() for t in ps])
+    pk, pv = P(kp), P(vp)
+    t0 = time.perf_counter()
+    rc = _lib.load().adkv_decode_attn_ckpt(
+        q.data_ptr(), dk.data_ptr(), dv.data_ptr(), kn.data_ptr(), vn.data_ptr(), ctypes.addressof(pk), ctypes.addressof(pv),
+        None, None, kck.data_ptr(), vck.data_ptr(), iv, kck.shape[2], None, 0, out.data_ptr(), scratch.data_ptr(),
+        scratch.numel(), B, H, H, T, D, dk.shape[2], bits, 0.1, SMIN, SMAX, _lib.FLAG_SELFTEST_MUTE_K,
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert 0.9 < time.perf_counter() - t0 < 4.0
+    assert gemv.device_status() == 3                               # the wait for logits ran out
+    assert torch.isnan(out).all()                                  # marked, not stale
+    assert torch.equal(dk, before_k)                               # the muted K warps appended nothing
+    again = gemv.decode_attn(q, dk, dv, kn, vn, kp, vp, T, 0.1, SMIN, SMAX, bits=bits, k_ckpt=kck, v_ckpt=vck,
+                             ckpt_interval=iv, scratch=scratch)
+    assert torch.equal(again, good) and gemv.device_status() == 0  # the device still answers, and correctly

@@ -1,6 +1,7 @@
 """The reference's UNMODIFIED model file driving the three-function boundary, on CPU.
 
-Needs a checkout of the reference beside this repository (skipped otherwise, e.g. on a GPU box).  A stand-in
+Runs on a checkout of the reference beside this repository or, where there is none, on the copy of the model file
+that ``oracle/build_ref.py`` staged unchanged under ``oracle/_ref/src``.  A stand-in
 for the kernel module with the reference's three signatures, backed by the numpy oracle, is registered as
 ``adkv.kernel.gemv`` before ``adkv.hf.llama_adkv`` is imported; a tiny random-init model then runs
 ``generate``.  What is checked is the CONTRACT the CUDA path is written against: which calls the model
@@ -23,8 +24,19 @@ from oracle import adkv_oracle as orc
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.environ.get("ADKV_REFERENCE_ROOT", os.path.join(ROOT, os.pardir, "reference"))
-pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(REF, "src", "adkv", "hf", "llama_adkv.py")),
-                                reason="reference checkout not present")
+
+
+def _reference_src():
+    """The reference's ``src`` folder: the checkout when it is there, else the unchanged copy of the files this test
+    executes that oracle/build_ref.py staged under oracle/_ref/src (which travels to machines without a checkout)."""
+    from oracle import build_ref
+    if os.path.exists(os.path.join(REF, "src", "adkv", "hf", "llama_adkv.py")):
+        return os.path.join(REF, "src")
+    return build_ref.staged_src()
+
+
+pytestmark = pytest.mark.skipif(_reference_src() is None,
+                                reason="neither a reference checkout nor its staged copy is present")
 
 
 def _np(ps):
@@ -75,7 +87,7 @@ def clean_reference_modules():
 def test_reference_model_file_drives_the_boundary_as_documented(monkeypatch, clean_reference_modules):
     from transformers import LlamaConfig
     calls = []
-    monkeypatch.syspath_prepend(os.path.join(REF, "src"))
+    monkeypatch.syspath_prepend(_reference_src())
     for name in [m for m in sys.modules if m == "adkv" or m.startswith("adkv.")]:
         monkeypatch.delitem(sys.modules, name)
     import adkv.kernel as kernel_pkg                                   # the reference's package (empty __init__)
