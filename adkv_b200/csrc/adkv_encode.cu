@@ -13,11 +13,9 @@ namespace adkv {
 // (half2 per lane) and per supergroup it writes 256 contiguous bytes (uint2 per lane).  The next
 // word's tokens are fetched while the current word is quantised.
 constexpr int kEncThreads = kD / 2;
-#ifndef ADKV_ENC_STAGES
-#define ADKV_ENC_STAGES 3
-#endif
-constexpr int kEncStages = ADKV_ENC_STAGES;   // 32-token (8 KB) tiles of fp16 input in flight per CTA; 24 KB lets 7+ CTAs share an SM,
-                                // so K and V of 512 streams (1024 CTAs) run as a single wave on 148 SMs
+constexpr int kEncStages = 2;   // 32-token (8 KB) tiles of fp16 input in flight per CTA.  16 KB per CTA lets 14 CTAs share an SM,
+                                // which is what a launch over several layers needs (8 layers: 0.645 ms per layer with 2
+                                // stages, 0.688 ms with 3); K and V of one layer are 6.9 CTAs per SM either way (0.86 ms)
 
 // Eight tokens for the two channels of a thread,
 // speculative quantiser (see quantize_spec) on the channel pair with packed fp32 arithmetic: half the

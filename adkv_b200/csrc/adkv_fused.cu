@@ -62,8 +62,8 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
 using namespace adkv;
 
 // adkv_decode_attn splits the channels of a head over two warp pairs up to this many (batch, kv head) streams per
-// launch: measured on a B200 (4096 tokens, 4-bit) the split wins only while there is at most about one stream per
-// SM (128 streams: 200 us against 216 us); from 256 streams on the whole-head kernel is faster (512 streams:
+// launch: measured on a B200 (4096 tokens, 4-bit) the split is no slower only while there is at most about one
+// stream per SM (128 streams: 200 us either way); from 256 streams on the whole-head kernel is faster (512 streams:
 // 274 us against 324 us), because the split costs a quarter more instructions and both are then bound by issue.
 constexpr long long kSplitChannelsMaxStreams = 160;
 
