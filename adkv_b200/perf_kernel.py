@@ -1,6 +1,6 @@
 """Decode-step kernel micro-benchmark on the grid and with the methodology of the reference's own tool.
 
-    python -m adkv_b200.perf_kernel [--impl trio,fused,fused-fast,trio-half,fused-half,reference] [--reference-so PATH]
+    python -m adkv_b200.perf_kernel [--impl trio,fused,fused-fast,fused-tail,trio-half,fused-half,reference] [--reference-so PATH]
                                     [--json out.json]
 
 The reference measures one decode step of one layer (``forward_qk`` -> torch softmax -> ``forward_ov``) for
@@ -11,6 +11,9 @@ its published table is for an L40).  This tool repeats that on the GPU it runs o
 * ``trio``       the same three calls through this library (drop-in signatures),
 * ``fused``      the single-launch ``decode_attn`` that replaces them,
 * ``fused-fast`` the same with the contracted replay of the fp32 recurrence (``fast=True``),
+* ``fused-tail`` the same next to persisted tail states, as the cache object runs it: the appended code is quantised
+                 from the tail (bit-exact) and the replay is contracted; the tails are kept unadvanced so that every
+                 step overwrites slot T like the other columns,
 * ``*-half``     both in the fp16-state arithmetic of the reference's CUDA kernels,
 * ``reference``  the reference's own kernels, from the extension module given with ``--reference-so`` (the
                  ``adkv_gemv`` module the reference JIT-builds, or the one ``oracle/build_ref.py`` compiles for
@@ -38,7 +41,7 @@ NH, DIM = 32, 128
 BATCHES = [1, 4, 16, 32, 64, 128, 256, 512]
 SEQ_LENS = [128, 256, 512, 1024, 2048]
 LAYERS = 32
-IMPLS = ("trio", "fused", "fused-fast", "trio-half", "fused-half", "reference")
+IMPLS = ("trio", "fused", "fused-fast", "fused-tail", "trio-half", "fused-half", "reference")
 
 
 def load_extension(path: str):
@@ -73,10 +76,17 @@ def make_step(impl: str, B: int, T: int, dev, ref=None):
             gemv.forward_ov(torch.softmax(logits, dim=-1), vc, vn, *p, SCALE_MIN, SCALE_MAX, half_state=half)
     else:
         out = torch.empty(B, NH, DIM, dtype=torch.float16, device=dev)
+        tails = {}
+        if impl == "fused-tail":    # state after the cached tokens: zero point 0 (the codes are all 2: q * scale accumulates
+            # with alpha, but any finite state does for timing), scale 1 (beta is 0 here)
+            tk = torch.zeros(B, NH, 2, DIM, dtype=torch.float32, device=dev)
+            tk[:, :, 1] = 1.0
+            tails = dict(k_tail=tk, v_tail=tk.clone(), tail_keep=True)
 
         def step():
             gemv.decode_attn(q, kc, vc, kn, vn, p, p, T, 1.0, SCALE_MIN, SCALE_MAX, half_state=half,
-                             fast=impl == "fused-fast", out=out)
+                             fast=True if impl == "fused-fast" else None if impl == "fused-tail" else False, out=out,
+                             **tails)
     return step
 
 

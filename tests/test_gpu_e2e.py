@@ -205,12 +205,12 @@ def test_half_state_generation_fused_and_trio_agree():
 def test_kernel_benchmark_tool_runs_on_a_small_grid(tmp_path):
     from adkv_b200 import perf_kernel
     from oracle import ref_cuda
-    argv = ["--impl", "trio,fused,fused-fast,trio-half,fused-half,reference", "--batches", "2,3", "--seq-lens", "128,200",
+    argv = ["--impl", "trio,fused,fused-fast,fused-tail,trio-half,fused-half,reference", "--batches", "2,3", "--seq-lens", "128,200",
             "--json", str(tmp_path / "grid.json")]
     if ref_cuda.available():
         argv += ["--reference-so", ref_cuda.PATH]
     table = perf_kernel.main(argv)
-    want = {"trio", "fused", "fused-fast", "trio-half", "fused-half"} | ({"reference"} if ref_cuda.available() else set())
+    want = {"trio", "fused", "fused-fast", "fused-tail", "trio-half", "fused-half"} | ({"reference"} if ref_cuda.available() else set())
     assert set(table) == want
     for rows in table.values():
         assert set(rows) == {2, 3} and all(r[T]["req_per_s"] > 0 for r in rows.values() for T in (128, 200))

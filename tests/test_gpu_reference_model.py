@@ -145,7 +145,7 @@ def test_reference_model_file_end_to_end_throughput(reference_model_module):
     (HF ``generate``, its cache object, qk -> torch softmax -> ov per layer) on this library's kernels: batch 128,
     prompt 1024, as the end-to-end benchmark configuration, with a short generation.  The decode rate is the
     difference of two runs (17 and 1 new tokens; method of the reference's tools/perf_e2e.py:102-113: wall
-    time around ``generate``).  Report only; written to gpurun_out/ when that folder exists."""
+    time around ``generate``).  Report only; also written as JSON into the folder ``ADKV_RESULTS_DIR`` names, if set."""
     M = reference_model_module
     from transformers import LlamaConfig
     if torch.cuda.get_device_properties(0).total_memory < 100e9:
@@ -182,8 +182,8 @@ def test_reference_model_file_end_to_end_throughput(reference_model_module):
            "batch": B, "prompt": prompt, "decode_ms_per_step": step_ms, "decode_tokens_per_s": B / (step_ms * 1e-3),
            "prefill_plus_first_token_s": t1}
     print(json.dumps(res))
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("ADKV_RESULTS_DIR", "")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "e2e_reference_model_file.json"), "w") as f:
             json.dump(res, f)
     assert step_ms > 0
