@@ -277,6 +277,28 @@ __device__ __forceinline__ void append_new_token(Chan (&ch)[4], const ParamPtrs 
     if (ckpt_out) store_state(ckpt_out, ch, c0, D);
 }
 
+struct Chan4 {
+    Chan c[4];
+};
+
+// The guarded, possibly partial chunk as a real function call.  It runs where a scale sits near a clamp bound (or
+// under the eps guard) and for the ragged last tile of a stream: rarely.  Inlined next to the packed fast path it
+// made the scan loops large enough to miss the instruction cache on every tile; as a call the loops hold only the
+// fast path.  State and operands travel by value (registers, or the call stack past the ABI's register limit).
+template <int G>
+struct QueryRegs {
+    float v[G][4];
+};
+template <int BITS, int G, bool EXACT>
+__device__ __noinline__ Chan4 k_chunk_guarded(uint4 w, Chan4 st, QueryRegs<G> q, float *red, int lane, int count,
+                                              float smin, float smax)
+{
+    FieldConsts<BITS> fc;
+    fc.init();
+    k_chunk<BITS, G, EXACT, true, true>(w, fc, st.c, q.v, red, lane, count, smin, smax);
+    return st;
+}
+
 // Sink interface (duck-typed):
 //   bool begin_tile(int i)            wait for room; false = bounded wait gave up
 //   void put8(int i, int g, int tok_in_tile, float v, int lane)   called by lanes 0..7 with tok = base + lane
@@ -318,6 +340,23 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
                           (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait, row_stride};
     ring.prologue(lane);
 
+    auto guarded = [&](const uint4 &w, int count) {
+        Chan4 st;
+        QueryRegs<G> qr;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) st.c[c] = ch[c];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) qr.v[g][c] = qv[g][c];
+        st = k_chunk_guarded<BITS, G, EXACT>(w, st, qr, red, lane, count, a.smin, a.smax);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            ch[c].zp = st.c[c].zp;
+            ch[c].s = st.c[c].s;
+        }
+    };
+
     bool ok = true;
     int i = 0;
     for (; i < ring.n_tiles; ++i) {
@@ -336,7 +375,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     if (safe.holds(ch)) k_chunk2<BITS, G, EXACT>(w, fc, ch, pc, one, qv2, red, lane);
-                    else k_chunk<BITS, G, EXACT, false, true>(w, fc, ch, qv, red, lane, 8, a.smin, a.smax);
+                    else guarded(w, 8);
                     reduce8<G>(red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
@@ -351,7 +390,7 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
                 const int count = ntok - wd * C::TPW;   // valid fields in this word (may exceed TPW)
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
-                    k_chunk<BITS, G, EXACT, true, true>(w, fc, ch, qv, red, lane, count - c8 * 8, a.smin, a.smax);
+                    guarded(w, count - c8 * 8);
                     reduce8<G>(red, lane, sum);
 #pragma unroll
                     for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
@@ -496,6 +535,23 @@ __device__ __forceinline__ void src_give_up(S &, int, long) {}
 //   bool self_weight(int lane, float (&acc)[G][4], float (&w_self)[G], int T)
 //   void store(const VArgs&, int b, int h, int c0, const float (&acc)[G][4])   write the result (c0: first channel)
 //   void give_up(int c0)              optional: called instead of store() when a bounded wait gave up
+
+// v_chunk's guarded, possibly partial form as a real function call (see k_chunk_guarded).
+template <int G>
+struct VState {
+    Chan c[4];
+    float acc[G][4];
+};
+template <int BITS, int G, bool EXACT>
+__device__ __noinline__ VState<G> v_chunk_guarded(uint4 w, VState<G> st, const float2 *wts, int tok0, int count,
+                                                  float smin, float smax)
+{
+    FieldConsts<BITS> fc;
+    fc.init();
+    v_chunk<BITS, G, EXACT, true, true>(w, fc, st.c, wts, tok0, st.acc, count, smin, smax);
+    return st;
+}
+
 template <int BITS, int G, int ARITH, class Src, int STAGES = kStages, bool WIDE = false>
 __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                        uint64_t *ring_bar, const float2 *wts, Src &src)
@@ -527,6 +583,26 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
                           (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait, row_stride};
     ring.prologue(lane);
 
+    auto guarded = [&](const uint4 &w, int tok0, int count) {
+        VState<G> st;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) st.c[c] = ch[c];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) st.acc[g][c] = acc[g][c];
+        st = v_chunk_guarded<BITS, G, EXACT>(w, st, wts, tok0, count, a.smin, a.smax);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            ch[c].zp = st.c[c].zp;
+            ch[c].s = st.c[c].s;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[g][c] = st.acc[g][c];
+    };
+
     bool ok = true;
     int i = 0;
     for (; i < ring.n_tiles; ++i) {
@@ -543,7 +619,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
                 for (int c8 = 0; c8 < C::TPW / 8; ++c8) {
                     const int tok0 = wd * C::TPW + c8 * 8;
                     if (safe.holds(ch)) v_chunk2<BITS, G, EXACT>(w, fc, ch, pc, one, wts, tok0, acc);
-                    else v_chunk<BITS, G, EXACT, false, true>(w, fc, ch, wts, tok0, acc, 8, a.smin, a.smax);
+                    else guarded(w, tok0, 8);
                     if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }
                 w = w_next;
@@ -555,8 +631,7 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
                 const int count = ntok - wd * C::TPW;
 #pragma unroll 1
                 for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
-                    v_chunk<BITS, G, EXACT, true, true>(w, fc, ch, wts, wd * C::TPW + c8 * 8, acc, count - c8 * 8,
-                                                        a.smin, a.smax);
+                    guarded(w, wd * C::TPW + c8 * 8, count - c8 * 8);
                     if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; w.z >>= 16; w.w >>= 16; }
                 }
             }

@@ -250,8 +250,9 @@ struct SafeRange {
             float pmn = gmn * gmn, pmx = gmx * gmx;                          // 8th powers
             pmn *= pmn; pmn *= pmn;
             pmx *= pmx; pmx *= pmx;
-            const float l = gmn > 0.f ? fmaxf(smin, kEps) / (pmn * (1.f - 2e-5f)) : INFINITY;
-            const float h = smax / (pmx * (1.f + 2e-5f));
+            // approximate division (2 ulp) is far inside the 2e-5 margin that keeps the interval conservative
+            const float l = gmn > 0.f ? __fdividef(fmaxf(smin, kEps), pmn * (1.f - 2e-5f)) : INFINITY;
+            const float h = __fdividef(smax, pmx * (1.f + 2e-5f));
             lo = fmaxf(lo, l);
             hi = fminf(hi, h);
         }
@@ -260,8 +261,9 @@ struct SafeRange {
     // warp-uniform: every channel of every lane is inside its interval
     __device__ __forceinline__ bool holds(const Chan (&ch)[4]) const
     {
-        const float mn = fminf(fminf(ch[0].s, ch[1].s), fminf(ch[2].s, ch[3].s));
-        const float mx = fmaxf(fmaxf(ch[0].s, ch[1].s), fmaxf(ch[2].s, ch[3].s));
+        // chained, not a tree: the chain maps onto the three-input minimum / maximum instruction
+        const float mn = fminf(fminf(fminf(ch[0].s, ch[1].s), ch[2].s), ch[3].s);
+        const float mx = fmaxf(fmaxf(fmaxf(ch[0].s, ch[1].s), ch[2].s), ch[3].s);
         return __all_sync(kFull, mn >= lo && mx <= hi);
     }
     __device__ __forceinline__ bool holds(const Chan (&ch)[2]) const
