@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
     const Seg seg{0, ka.T, true, nullptr, nullptr, 0};
     if (warp == 0) {
         RingSink<G> sink{&fs, 0, 0};
-        k_warp<BITS, G, ARITH>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
+        k_warp<BITS, G, ARITH, RingSink<G>, kStages, false, G == 1>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         SoftmaxSrc<G> src;
         src.sh = &fs;
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
         src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
         src.t_begin = 0;
         src.init();
-        v_warp<BITS, G, ARITH>(va, seg, b, h, lane, vbuf, vbar, wts, src);
+        v_warp<BITS, G, ARITH, SoftmaxSrc<G>, kStages, false, G == 1>(va, seg, b, h, lane, vbuf, vbar, wts, src);
     }
 }
 

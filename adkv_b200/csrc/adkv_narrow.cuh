@@ -205,23 +205,6 @@ __device__ __forceinline__ void k_chunk_n(const uint2 &w, Chan (&ch)[2], const f
     }
 }
 
-// The guarded, possibly partial chunk as a real function call (rare: a scale near a clamp bound, or the ragged
-// last tile), so that the scan loop holds only the packed fast path and stays in the instruction cache.
-struct Chan2 {
-    Chan c[2];
-};
-template <int G>
-struct QueryRegs2 {
-    float v[G][2];
-};
-template <int BITS, int G, bool EXACT>
-__device__ __noinline__ Chan2 k_chunk_n_guarded(uint2 w, Chan2 st, QueryRegs2<G> q, float *red, int lane, int count,
-                                                float smin, float smax)
-{
-    k_chunk_n<BITS, G, EXACT>(w, st.c, q.v, red, lane, count, smin, smax);
-    return st;
-}
-
 template <int BITS, int G, int ARITH, class Sink, int STAGES = kStages>
 __device__ __forceinline__ void k_warp_n(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
                                          uint64_t *ring_bar, float *red, Sink &sink)
@@ -256,24 +239,6 @@ __device__ __forceinline__ void k_warp_n(const KArgs &a, const Seg &seg, int b, 
                                   (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait};
     ring.prologue(lane);
 
-    auto guarded = [&](const uint2 &w, int count) {
-        Chan2 st;
-        QueryRegs2<G> qr;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) st.c[c] = ch[c];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            qr.v[g][0] = qv[g][0];
-            qr.v[g][1] = qv[g][1];
-        }
-        st = k_chunk_n_guarded<BITS, G, EXACT>(w, st, qr, red, lane, count, a.smin, a.smax);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            ch[c].zp = st.c[c].zp;
-            ch[c].s = st.c[c].s;
-        }
-    };
-
     bool ok = true;
     int i = 0;
     for (; i < ring.n_tiles; ++i) {
@@ -289,7 +254,7 @@ __device__ __forceinline__ void k_warp_n(const KArgs &a, const Seg &seg, int b, 
 #pragma unroll 1
             for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
                 if (count - c8 * 8 >= 8 && safe.holds(ch)) k_chunk_n2<BITS, G, EXACT>(w, fc, ch, pc, one, qv2, red, lane);
-                else guarded(w, count - c8 * 8);
+                else k_chunk_n<BITS, G, EXACT>(w, ch, qv, red, lane, count - c8 * 8, a.smin, a.smax);
                 reduce8<G>(red, lane, sum);
 #pragma unroll
                 for (int g = 0; g < G; ++g) sink.put8(i, g, wd * C::TPW + c8 * 8, sum[g], lane);
@@ -385,20 +350,6 @@ __device__ __forceinline__ void narrow(const float (&a4)[G][4], float (&a2)[G][2
     for (int g = 0; g < G; ++g) { a2[g][0] = a4[g][0]; a2[g][1] = a4[g][1]; }
 }
 
-// v_chunk_n as a real function call (see k_chunk_n_guarded).
-template <int G>
-struct VState2 {
-    Chan c[2];
-    float acc[G][2];
-};
-template <int BITS, int G, bool EXACT>
-__device__ __noinline__ VState2<G> v_chunk_n_guarded(uint2 w, VState2<G> st, const float2 *wts, int tok0, int count,
-                                                     float smin, float smax)
-{
-    v_chunk_n<BITS, G, EXACT>(w, st.c, wts, tok0, st.acc, count, smin, smax);
-    return st;
-}
-
 // Src: SoftmaxSrc<G, 2> (tile_weights, self_weight, norm).  The result is written here: two channels per lane.
 template <int BITS, int G, int ARITH, class Src, int STAGES = kStages>
 __device__ __forceinline__ void v_warp_n(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *ring_buf,
@@ -431,28 +382,6 @@ __device__ __forceinline__ void v_warp_n(const VArgs &a, const Seg &seg, int b, 
                                   (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait};
     ring.prologue(lane);
 
-    auto guarded = [&](const uint2 &w, int tok0, int count, float (&acc)[G][2]) {
-        VState2<G> st;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) st.c[c] = ch[c];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            st.acc[g][0] = acc[g][0];
-            st.acc[g][1] = acc[g][1];
-        }
-        st = v_chunk_n_guarded<BITS, G, EXACT>(w, st, wts, tok0, count, a.smin, a.smax);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            ch[c].zp = st.c[c].zp;
-            ch[c].s = st.c[c].s;
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            acc[g][0] = st.acc[g][0];
-            acc[g][1] = st.acc[g][1];
-        }
-    };
-
     bool ok = true;
     int i = 0;
     for (; i < ring.n_tiles; ++i) {
@@ -470,7 +399,7 @@ __device__ __forceinline__ void v_warp_n(const VArgs &a, const Seg &seg, int b, 
             for (int c8 = 0; c8 < C::TPW / 8 && c8 * 8 < count; ++c8) {
                 const int tok0 = wd * C::TPW + c8 * 8;
                 if (count - c8 * 8 >= 8 && safe.holds(ch)) v_chunk_n2<BITS, G, EXACT>(w, fc, ch, pc, one, wts, tok0, acc);
-                else guarded(w, tok0, count - c8 * 8, acc);
+                else v_chunk_n<BITS, G, EXACT>(w, ch, wts, tok0, acc, count - c8 * 8, a.smin, a.smax);
                 if (C::TPW == 16) { w.x >>= 16; w.y >>= 16; }
             }
         }
