@@ -319,6 +319,12 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
     const int bh = b * a.Hkv + h;
     const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
     const int c0 = kD * slice + 4 * lane;      // first of this lane's 4 channels within the head
+    const uint32_t row_stride = uint32_t(D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
+    const int n_tok = seg.t_end - seg.t_begin;
+    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait, row_stride};
+    ring.prologue(lane);   // first: the copies of the first tiles fly while the parameters below are loaded
     Chan ch[4];
     SafeRange safe;
     FieldConsts<BITS> fc;
@@ -338,12 +344,6 @@ __device__ __forceinline__ void k_warp(const KArgs &a, const Seg &seg, int b, in
         qv2[g][1] = pk2(qv[g][2], qv[g][3]);
     }
 
-    const uint32_t row_stride = uint32_t(D) * 4;
-    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
-    const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
-                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatKWait, row_stride};
-    ring.prologue(lane);
 
     auto guarded = [&](const uint4 &w, int count, auto partial_tag) {
         if constexpr (!OUTLINE) {
@@ -570,6 +570,12 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
     const int bh = b * a.Hkv + h;
     const int D = WIDE ? a.D : kD, slice = WIDE ? seg.slice : 0;
     const int c0 = kD * slice + 4 * lane;
+    const uint32_t row_stride = uint32_t(D) * 4;
+    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
+    const int n_tok = seg.t_end - seg.t_begin;
+    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
+                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait, row_stride};
+    ring.prologue(lane);   // first: the copies of the first tiles fly while the parameters below are loaded
     Chan ch[4];
     SafeRange safe;
     FieldConsts<BITS> fc;
@@ -585,12 +591,6 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
 
-    const uint32_t row_stride = uint32_t(D) * 4;
-    uint8_t *stream = a.cache + (size_t(bh) * a.n_super_cap * D + size_t(kD) * slice) * 4;
-    const int n_tok = seg.t_end - seg.t_begin;
-    StreamRing<BITS, STAGES, WIDE> ring{ring_buf, ring_bar, stream + size_t(seg.t_begin / C::TPW) * row_stride,
-                          (n_tok + kTileTok - 1) / kTileTok, n_tok, kStatVWait, row_stride};
-    ring.prologue(lane);
 
     auto guarded = [&](const uint4 &w, int tok0, int count, auto partial_tag) {
         if constexpr (!OUTLINE) {
@@ -658,12 +658,12 @@ __device__ __forceinline__ void v_warp(const VArgs &a, const Seg &seg, int b, in
     }
 
     if (seg.append) {
+        float xh[4];
         float w_self[G];
         if (!src.self_weight(lane, acc, w_self, a.T)) {
             src_give_up(src, c0, 0);
             return;
         }
-        float xh[4];
         append_new_token<BITS, ARITH>(ch, a.p, size_t(h) * D + c0, a.tail ? a.tail + size_t(bh) * 2 * D : nullptr,
                                       a.tail_keep, a.x_new + size_t(bh) * D + c0,
                                       reinterpret_cast<uint4 *>(stream + size_t(a.T / C::TPW) * row_stride) + lane, a.T,
