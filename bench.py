@@ -9,7 +9,8 @@ codes.  With N > 1 (one process per GPU, launched by torch.distributed.run) the 
 of that fixed workload are sharded over the ranks (``adkv_b200.sharding``: whole sequences first, KV heads
 when the batch does not divide) with no collective on the data path: strong scaling.  ``--scaling weak``
 gives every rank the whole workload instead; with the default the weak figure is measured too and printed
-as the extra key ``weak_scaling``.  Rank 0 prints one JSON line.
+as the extra key ``weak_scaling``, and the same shards with state checkpoints as
+``strong_with_checkpoints``.  Rank 0 prints one JSON line.
 
 ``value``  : packed-KV bytes processed per second by the whole job, inputs resident in HBM.
 ``e2e``    : the same through the public Python API with the step's q / k_new / v_new coming from
@@ -45,6 +46,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+
+STRONG_CKPT_INTERVAL = 512     # tokens between state checkpoints in the `strong_with_checkpoints` figure
 
 WORKLOADS = {
     # name: per-GPU batch, q heads, kv heads, head dim, cached tokens, bits
@@ -836,13 +839,21 @@ def run_ours(args, w, name):
         weak_ms = decode_ms(w_global, args.replay if args.replay in ("tail", "exact", "fast") else "tail", torch, device,
                             max(1, min(args.steps, 30)), seed=3000 + 7919 * rank, ckpt_interval=args.ckpt_interval)
 
+    # and the same strong-scaling shard with state checkpoints (opt-in cache metadata that splits the token axis into
+    # independent segments): what a cache owner who knows that a GPU holds few streams would allocate
+    ckpt_ms = None
+    if world > 1 and args.scaling == "strong" and not args.no_weak and not args.ckpt_interval and args.replay == "tail":
+        ckpt_ms = decode_ms(w, "tail", torch, device, max(1, min(args.steps, 50)), seed=1000 + 7919 * rank,
+                            ckpt_interval=STRONG_CKPT_INTERVAL)
+
     bytes_rank = algorithmic_bytes(w)
     bytes_job = bytes_rank
     if world > 1:
-        t = torch.tensor([total_ms, e2e_ms, weak_ms or 0.0] + [ms for _, ms in others], dtype=torch.float64, device=device)
+        t = torch.tensor([total_ms, e2e_ms, weak_ms or 0.0, ckpt_ms or 0.0] + [ms for _, ms in others],
+                         dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, weak_ms = t.tolist()[:3]
-        others = [[m, v] for (m, _), v in zip(others, t.tolist()[3:])]
+        total_ms, e2e_ms, weak_ms, ckpt_ms = t.tolist()[:4]
+        others = [[m, v] for (m, _), v in zip(others, t.tolist()[4:])]
         nb = torch.tensor([bytes_rank, B], dtype=torch.float64, device=device)
         dist.all_reduce(nb, op=dist.ReduceOp.SUM)
         bytes_job, seqs_job = nb.tolist()
@@ -882,6 +893,12 @@ def run_ours(args, w, name):
             res["weak_scaling"] = {"ms_per_step": weak_ms, "value": wb / (weak_ms * 1e-3) / 1e9, "unit": UNIT,
                                    "global_batch": w_global["B"] * world,
                                    "what": "every rank runs the whole workload (per-GPU work fixed)"}
+        if ckpt_ms:
+            res["strong_with_checkpoints"] = {
+                "ms_per_step": ckpt_ms, "value": bytes_job / (ckpt_ms * 1e-3) / 1e9, "unit": UNIT,
+                "ckpt_interval": STRONG_CKPT_INTERVAL,
+                "what": "the same shards with state checkpoints every %d tokens (adkv_decode_attn_ckpt: segments of a "
+                        "stream run on separate warp pairs, one more launch merges them)" % STRONG_CKPT_INTERVAL}
         res.update(trio_legs)
         if world == 1 and not args.no_cpu and half:
             res["parity_check"] = "ok" if check_half(w, st, out) else "FAILED"
