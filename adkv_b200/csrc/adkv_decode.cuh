@@ -288,7 +288,7 @@ struct Chan4 {
 // fast path.  State and operands travel by value in registers.  Opt-in per kernel (template parameter OUTLINE of
 // k_warp / v_warp): a call changes the register allocation of the whole kernel, and with more than two query heads per
 // KV head the operands no longer fit the registers of the calling convention, which would move the accumulators to
-// local memory for the whole scan.  The fused whole-head kernel with one query head per KV head uses it (measured:
+// local memory for the whole scan.  The fused whole-head kernel uses it for 4-bit codes with one query head per KV head (measured:
 // 15 % faster at 128-token contexts, no change at 4096).
 template <int G>
 struct QueryRegs {

@@ -9,6 +9,13 @@ namespace adkv {
 // =========================================================================================
 // Fused decode step: one CTA per (batch, kv head); warp 0 scans K, warp 1 scans V.
 
+// Whether the guarded chunk bodies of this instantiation are function calls (see k_chunk_guarded).  Measured on a
+// B200 against the inline form, streams of 32 heads x 128: 4-bit codes with one query head per KV head gain 13 % at
+// 128-token contexts and lose nothing elsewhere; 2-bit codes gain 17 % there but lose 7 % in the canonical replay and
+// 14 % with 512 streams per launch, so they keep the inline form, as do the instantiations with several query heads.
+template <int BITS, int G>
+constexpr bool kOutOfLineGuarded = BITS == 4 && G == 1;
+
 template <int BITS, int G, int ARITH>
 __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
                                                          long long mask_stride_b, float scaling,
@@ -43,7 +50,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
     const Seg seg{0, ka.T, true, nullptr, nullptr, 0};
     if (warp == 0) {
         RingSink<G> sink{&fs, 0, 0};
-        k_warp<BITS, G, ARITH, RingSink<G>, kStages, false, G == 1>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
+        k_warp<BITS, G, ARITH, RingSink<G>, kStages, false, kOutOfLineGuarded<BITS, G>>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         SoftmaxSrc<G> src;
         src.sh = &fs;
@@ -53,7 +60,7 @@ __global__ void __launch_bounds__(64) decode_attn_kernel(KArgs ka, VArgs va, con
         src.n_tiles = (va.T + kTileTok - 1) / kTileTok;
         src.t_begin = 0;
         src.init();
-        v_warp<BITS, G, ARITH, SoftmaxSrc<G>, kStages, false, G == 1>(va, seg, b, h, lane, vbuf, vbar, wts, src);
+        v_warp<BITS, G, ARITH, SoftmaxSrc<G>, kStages, false, kOutOfLineGuarded<BITS, G>>(va, seg, b, h, lane, vbuf, vbar, wts, src);
     }
 }
 
