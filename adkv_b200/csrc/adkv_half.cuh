@@ -471,20 +471,20 @@ __device__ __forceinline__ void v_warp_h(const VArgs &a, const Seg &seg, int b, 
 // recurrence (adkv_decode.cuh); 2 = the fp16-state arithmetic above.
 constexpr int kModeHalf = 2;
 
-template <int BITS, int G, int MODE, class Sink, int ST = kStages, bool WIDE = false>
+template <int BITS, int G, int MODE, class Sink, int ST = kStages, bool WIDE = false, bool OUTLINE = false>
 __device__ __forceinline__ void k_scan(const KArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
                                        float *red, Sink &sink)
 {
     if constexpr (MODE == kModeHalf) k_warp_h<BITS, G, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
-    else k_warp<BITS, G, MODE, Sink, ST, WIDE>(a, seg, b, h, lane, buf, bar, red, sink);
+    else k_warp<BITS, G, MODE, Sink, ST, WIDE, OUTLINE>(a, seg, b, h, lane, buf, bar, red, sink);
 }
 
-template <int BITS, int G, int MODE, class Src, int ST = kStages, bool WIDE = false>
+template <int BITS, int G, int MODE, class Src, int ST = kStages, bool WIDE = false, bool OUTLINE = false>
 __device__ __forceinline__ void v_scan(const VArgs &a, const Seg &seg, int b, int h, int lane, uint8_t *buf, uint64_t *bar,
                                        const float2 *wts, Src &src)
 {
     if constexpr (MODE == kModeHalf) v_warp_h<BITS, G, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
-    else v_warp<BITS, G, MODE, Src, ST, WIDE>(a, seg, b, h, lane, buf, bar, wts, src);
+    else v_warp<BITS, G, MODE, Src, ST, WIDE, OUTLINE>(a, seg, b, h, lane, buf, bar, wts, src);
 }
 
 }  // namespace adkv

@@ -54,6 +54,11 @@ struct CkptArgs {
     bool mute_k;              // self-test (ADKV_FLAG_SELFTEST_MUTE_K): the K warps do nothing, so every V warp's wait runs out
 };
 
+// Guarded chunk bodies as function calls (see k_chunk_guarded): measured 2-3 % faster for 4-bit codes with one query
+// head per KV head at every batch and checkpoint interval tried; not measured for the other instantiations.
+template <int BITS, int G>
+constexpr bool kOutOfLineGuardedSegments = BITS == 4 && G == 1;
+
 template <int BITS, int G, int MODE>
 __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs va, const float *__restrict__ mask,
                                                                long long mask_stride_b, float scaling, CkptArgs ck,
@@ -90,7 +95,7 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
         seg.init = j ? ck.k_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
         seg.ckpt_out = write_ckpt ? ck.k_ckpt + out_idx * 2 * kD : nullptr;
         RingSink<G> sink{&fs, 0, 0};
-        k_scan<BITS, G, MODE>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
+        k_scan<BITS, G, MODE, RingSink<G>, kStages, false, kOutOfLineGuardedSegments<BITS, G>>(ka, seg, b, h, lane, kbuf, kbar, red, sink);
     } else {
         seg.init = j ? ck.v_ckpt + (stream_ckpt + j - 1) * 2 * kD : nullptr;
         seg.ckpt_out = write_ckpt ? ck.v_ckpt + out_idx * 2 * kD : nullptr;
@@ -103,7 +108,7 @@ __global__ void __launch_bounds__(64) decode_attn_split_kernel(KArgs ka, VArgs v
         src.t_begin = seg.t_begin;
         src.part = scratch + (size_t(bh) * n_seg + j) * G * kPartStride;
         src.init();
-        v_scan<BITS, G, MODE>(va, seg, b, h, lane, vbuf, vbar, wts, src);
+        v_scan<BITS, G, MODE, PartialSrc<G, MODE == kModeHalf>, kStages, false, kOutOfLineGuardedSegments<BITS, G>>(va, seg, b, h, lane, vbuf, vbar, wts, src);
     }
 }
 
