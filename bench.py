@@ -771,14 +771,22 @@ def run_ours(args, w, name):
     assert gemv.device_status(device) == 0, "a kernel gave up on a bounded wait"
 
     # ---- end to end through the public API: host inputs in, host output back, every step
-    hq, hk, hv = (t.cpu().pin_memory() for t in (st["q"], st["kn"], st["vn"]))
+    # the step's q, k_new and v_new sit back to back in one pinned staging buffer and travel in one copy
+    srcs = (st["q"], st["kn"], st["vn"])
+    n_in = sum(t.numel() for t in srcs)
+    h_in = torch.empty(n_in, dtype=torch.float16).pin_memory()
+    d_in = torch.empty(n_in, dtype=torch.float16, device=device)
+    views, off = [], 0
+    for t in srcs:
+        h_in[off:off + t.numel()].copy_(t.reshape(-1))
+        views.append(d_in[off:off + t.numel()].view(t.shape))
+        off += t.numel()
+    dq, dk_, dv_ = views
+    hq, hk, hv = srcs                       # sizes for the byte count below
     hout = torch.empty((B, Hq, D), dtype=torch.float16).pin_memory()
-    dq, dk_, dv_ = (torch.empty_like(t) for t in (st["q"], st["kn"], st["vn"]))
 
     def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk_.copy_(hk, non_blocking=True)
-        dv_.copy_(hv, non_blocking=True)
+        d_in.copy_(h_in, non_blocking=True)
         gemv.decode_attn(dq, st["kc"], st["vc"], dk_, dv_, st["kp"], st["vp"], T, scaling,
                          synth.SCALE_MIN, synth.SCALE_MAX, bits=bits, out=out, **headline, **ck)
         hout.copy_(out, non_blocking=True)
