@@ -15,8 +15,36 @@ import sys
 import types
 
 
-def install(force: bool = True):
-    """Register adkv_b200.gemv as ``adkv.kernel.gemv``; returns the module."""
+def _reference_cuda_arithmetic():
+    """A module with the three entry points bound to the arithmetic of the reference's CUDA kernels (fp16 state and
+    accumulation, ``src/adkv/kernel/gemv.cu``): packed caches bit-identical to what the reference's own extension
+    writes, which the fp32 recurrence of its torch code (this package's default) does not give."""
+    from . import gemv
+    mod = types.ModuleType("adkv.kernel.gemv")
+    mod.__doc__ = "adkv_b200.gemv with half_state=True behind the reference's three entry points"
+
+    def encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min, scale_max):
+        return gemv.encode_kv(kv_cache, kv_new, kv_zp, kv_sc, kv_alpha, kv_beta, kv_t, scale_min, scale_max,
+                              half_state=True)
+
+    def forward_qk(q, k_cache, k_new, k_zp, k_sc, k_alpha, k_beta, k_t, T, scale_min, scale_max):
+        return gemv.forward_qk(q, k_cache, k_new, k_zp, k_sc, k_alpha, k_beta, k_t, T, scale_min, scale_max,
+                               half_state=True)
+
+    def forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min, scale_max):
+        return gemv.forward_ov(attn, v_cache, v_new, v_zp, v_sc, v_alpha, v_beta, v_t, scale_min, scale_max,
+                               half_state=True)
+
+    mod.encode_kv, mod.forward_qk, mod.forward_ov = encode_kv, forward_qk, forward_ov
+    return mod
+
+
+def install(force: bool = True, half_state: bool = False):
+    """Register the kernels as ``adkv.kernel.gemv``; returns the registered module.
+
+    ``half_state=False``: :mod:`adkv_b200.gemv` itself (fp32 recurrence in the order of the reference's torch code).
+    ``half_state=True``: the same entry points in the arithmetic of the reference's CUDA kernels, for a deployment
+    that has to reproduce, bit for bit, the caches its reference build wrote."""
     from . import gemv
     for name in ("adkv", "adkv.kernel"):
         if name not in sys.modules:
@@ -26,10 +54,11 @@ def install(force: bool = True):
                 pkg = types.ModuleType(name)
                 pkg.__path__ = []                      # namespace stand-in when the reference is absent
                 sys.modules[name] = pkg
+    mod = _reference_cuda_arithmetic() if half_state else gemv
     if force or "adkv.kernel.gemv" not in sys.modules:
-        sys.modules["adkv.kernel.gemv"] = gemv
-        setattr(sys.modules["adkv.kernel"], "gemv", gemv)
-    return gemv
+        sys.modules["adkv.kernel.gemv"] = mod
+        setattr(sys.modules["adkv.kernel"], "gemv", mod)
+    return sys.modules["adkv.kernel.gemv"]
 
 
 def patch_mask_sizes(cache_layer_cls):

@@ -60,6 +60,25 @@ def test_positional_signatures_match_reference():
         assert all(p.default is not inspect.Parameter.empty for p in extra)     # extensions are optional
 
 
+def test_install_in_the_reference_kernels_arithmetic_keeps_the_positional_signatures():
+    saved = {k: sys.modules.get(k) for k in ("adkv", "adkv.kernel", "adkv.kernel.gemv")}
+    try:
+        mod = hf_shim.install(half_state=True)
+        assert importlib.import_module("adkv.kernel.gemv") is mod and mod is not gemv
+        for name in ("encode_kv", "forward_qk", "forward_ov"):
+            want = [p.name for p in inspect.signature(getattr(gemv, name)).parameters.values()
+                    if p.kind == p.POSITIONAL_OR_KEYWORD]
+            got = list(inspect.signature(getattr(mod, name)).parameters)
+            assert got == want, f"{name}: {got} != {want}"          # nothing but the reference's own arguments
+        assert hf_shim.install() is gemv                           # and the default registration comes back
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+
+
 def test_patch_mask_sizes_accepts_int_and_tensor():
     import torch
 

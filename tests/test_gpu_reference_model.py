@@ -23,7 +23,7 @@ import torch
 
 from adkv_b200 import gemv, hf_shim
 from oracle import adkv_oracle as orc
-from oracle import build_ref
+from oracle import build_ref, ref_cuda
 
 pytestmark = [pytest.mark.gpu,
               pytest.mark.skipif(build_ref.staged_src() is None,
@@ -79,6 +79,59 @@ class CheckedKernels:
         assert np.array_equal(v_cache.cpu().numpy(), want_cache), "forward_ov: appended code differs from the oracle's"
         self.calls.append(("forward_ov", tuple(v_cache.shape), attn.shape[2] - 1))
         return got
+
+
+class CheckedAgainstReferenceKernels:
+    """The three entry points in the arithmetic of the reference's CUDA kernels (``hf_shim.install(half_state=True)``),
+    each call repeated by the reference's own extension (``oracle/_ref/adkv_gemv.so``, its ``gemv.cu`` compiled for
+    sm_100a) on copies of the same inputs: caches bit for bit, outputs within fp16 accumulation-order noise."""
+
+    def __init__(self, ours, theirs):
+        self.ours, self.theirs = ours, theirs
+        self.n = 0
+        self.max_logit_err = self.max_out_err = 0.0
+
+    def encode_kv(self, kv_cache, kv_new, *rest):
+        want = kv_cache.clone()
+        self.theirs.encode_kv(want, kv_new, *rest)
+        out = self.ours.encode_kv(kv_cache, kv_new, *rest)
+        assert torch.equal(kv_cache, want), "encode_kv: packed cache differs from the reference kernel's"
+        self.n += 1
+        return out
+
+    def forward_qk(self, q, k_cache, k_new, *rest):
+        want_cache = k_cache.clone()
+        want = self.theirs.forward_qk(q, want_cache, k_new, *rest).float()
+        got = self.ours.forward_qk(q, k_cache, k_new, *rest)
+        assert torch.equal(k_cache, want_cache), "forward_qk: appended code differs from the reference kernel's"
+        assert got.shape == want.shape
+        tol = 2e-2 * max(1.0, float(want.abs().max()))
+        torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=tol)
+        self.max_logit_err = max(self.max_logit_err, float((got.float() - want).abs().max()))
+        self.n += 1
+        return got
+
+    def forward_ov(self, attn, v_cache, v_new, *rest):
+        want_cache = v_cache.clone()
+        want = self.theirs.forward_ov(attn, want_cache, v_new, *rest).view(attn.shape[0], attn.shape[1], -1).float()
+        got = self.ours.forward_ov(attn, v_cache, v_new, *rest)
+        assert torch.equal(v_cache, want_cache), "forward_ov: appended code differs from the reference kernel's"
+        torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2 * max(1.0, float(want.abs().max())))
+        self.max_out_err = max(self.max_out_err, float((got.float() - want).abs().max()))
+        self.n += 1
+        return got
+
+
+class ReferenceKernels:
+    """The reference's compiled extension behind the Python signatures of its ``adkv/kernel/gemv.py`` (a pass-through
+    there too, ``src/adkv/kernel/gemv.py:16-132``; only ``forward_ov`` reshapes its result)."""
+
+    def __init__(self, ext):
+        self.ext = ext
+        self.encode_kv, self.forward_qk = ext.encode_kv, ext.forward_qk
+
+    def forward_ov(self, attn, *rest):
+        return self.ext.forward_ov(attn, *rest).view(attn.shape[0], attn.shape[1], -1)
 
 
 @pytest.fixture
@@ -140,6 +193,32 @@ def test_reference_model_file_generates_on_the_cuda_kernels(reference_model_modu
           f"{checked.max_logit_err:.3e}, max |out - oracle| {checked.max_out_err:.3e}")
 
 
+@pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref/adkv_gemv.so has not been built")
+def test_reference_model_file_writes_the_caches_its_own_kernels_write(reference_model_module, monkeypatch):
+    """The same generation with ``hf_shim.install(half_state=True)``: every call the unmodified model file makes is
+    repeated by the reference's own CUDA kernels; the packed caches must be identical bit for bit after each call."""
+    M = reference_model_module
+    from transformers import LlamaConfig
+    checked = CheckedAgainstReferenceKernels(hf_shim.install(half_state=True), ReferenceKernels(ref_cuda.module()))
+    for fn in ("encode_kv", "forward_qk", "forward_ov"):
+        monkeypatch.setattr(M, fn, getattr(checked, fn))
+    torch.manual_seed(1)
+    L, H, Dh, B, prompt, new = 3, 4, 128, 3, 61, 8
+    cfg = LlamaConfig(hidden_size=H * Dh, intermediate_size=256, num_hidden_layers=L, num_attention_heads=H,
+                      num_key_value_heads=H, vocab_size=97, max_position_embeddings=256)
+    model = M.LlamaForCausalLM_ADKV(cfg).half().cuda().eval()
+    model.load_adkv_config([(_adkv_config(M, H * Dh, 30 + i), _adkv_config(M, H * Dh, 40 + i)) for i in range(L)])
+    ids = torch.randint(0, 97, (B, prompt), device="cuda")
+    with torch.no_grad():
+        out = model.generate(input_ids=ids, max_new_tokens=new, do_sample=False)
+    torch.cuda.synchronize()
+    assert gemv.device_status() == 0
+    assert out.shape == (B, prompt + new)
+    assert checked.n == 2 * L + 2 * L * (new - 1)
+    print(f"reference model file, reference-kernel arithmetic: {checked.n} calls equal the reference's own kernels "
+          f"(caches bit for bit; max |logit diff| {checked.max_logit_err:.3e}, max |out diff| {checked.max_out_err:.3e})")
+
+
 def test_reference_model_file_end_to_end_throughput(reference_model_module):
     """Decode tokens/s of the random-init Llama-2-7B architecture through the reference's unmodified model file
     (HF ``generate``, its cache object, qk -> torch softmax -> ov per layer) on this library's kernels: batch 128,
@@ -173,17 +252,28 @@ def test_reference_model_file_end_to_end_throughput(reference_model_module):
         assert out.shape == (B, prompt + new)
         return time.perf_counter() - t0
 
-    run(2)                                  # warm-up: allocator, cuBLAS handles
-    t1, t17 = run(1), run(17)
-    assert gemv.device_status() == 0
-    step_ms = (t17 - t1) / 16 * 1e3
+    kernel_sets = {"adkv_b200, fp32 recurrence (forward_qk -> torch softmax -> forward_ov)": hf_shim.install(),
+                   "adkv_b200, the reference kernels' arithmetic": hf_shim.install(half_state=True)}
+    if ref_cuda.available():
+        kernel_sets["the reference's own kernels compiled for sm_100a"] = ReferenceKernels(ref_cuda.module())
     res = {"what": "random-init Llama-2-7B architecture, HF generate through the reference's unmodified "
-                   "src/adkv/hf/llama_adkv.py on adkv_b200 kernels (forward_qk -> torch softmax -> forward_ov)",
-           "batch": B, "prompt": prompt, "decode_ms_per_step": step_ms, "decode_tokens_per_s": B / (step_ms * 1e-3),
-           "prefill_plus_first_token_s": t1}
+                   "src/adkv/hf/llama_adkv.py; only the three kernel entry points differ between the rows",
+           "batch": B, "prompt": prompt, "rows": {}}
+    for name, ks in kernel_sets.items():
+        for fn in ("encode_kv", "forward_qk", "forward_ov"):
+            setattr(M, fn, getattr(ks, fn))
+        run(2)                                  # warm-up: allocator, cuBLAS handles
+        t1, t17 = run(1), run(17)
+        assert gemv.device_status() == 0
+        step_ms = (t17 - t1) / 16 * 1e3
+        assert step_ms > 0
+        res["rows"][name] = {"decode_ms_per_step": step_ms, "decode_tokens_per_s": B / (step_ms * 1e-3),
+                             "prefill_plus_first_token_s": t1}
+    first = next(iter(res["rows"].values()))
+    res.update(decode_ms_per_step=first["decode_ms_per_step"], decode_tokens_per_s=first["decode_tokens_per_s"],
+               prefill_plus_first_token_s=first["prefill_plus_first_token_s"])
     print(json.dumps(res))
     out_dir = os.environ.get("ADKV_RESULTS_DIR", "")
     if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "e2e_reference_model_file.json"), "w") as f:
             json.dump(res, f)
-    assert step_ms > 0
